@@ -1,0 +1,296 @@
+// Element-wise and row-wise kernels of the step: embedding rows, residual sum + RMS norm,
+// position rotation + write into the paged cache, silu(gate)*up, arg-max and temperature sampling.
+// Every kernel exists for float32 and for bfloat16 storage; the arithmetic is float32 in both.
+//
+// What they replace in the reference (library calls there): F.embedding
+// (src/layers/embed_head.py:13), the RMS norm (src/layers/layernorm.py:12-23) and the residual
+// sums (src/models/llama.py:74-89), the rotation (src/layers/rotary_embedding.py:29-54), the
+// per-token cache writes (src/distengine/paged_kv_cache.py:162-175,311-312), silu*up
+// (src/layers/activation.py:8-9) and arg-max (src/layers/sampler.py:8).
+
+#include "common.cuh"
+
+// ------------------------------------------------------------------------------------------
+// embedding: out[n, :] = float(table[ids[n], :])           (the residual stream starts here)
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_rows_kernel(const int* __restrict__ ids, const T* __restrict__ table,
+                                  float* __restrict__ out, int width, int vocab) {
+    const int n = blockIdx.x;
+    int id = ids[n];
+    if (id < 0 || id >= vocab) id = 0;          // ids are validated on the host; never read outside
+    const T* row = table + (size_t)id * width;
+    float* dst = out + (size_t)n * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = to_float(row[i]);
+}
+
+DE_EXPORT int de_embed_rows(int dtype, const int* ids, const void* table, float* out, int n,
+                            int width, int vocab, void* stream) {
+    if (n <= 0) return 0;
+    const int threads = width >= 1024 ? 256 : 128;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == DE_BF16)
+        embed_rows_kernel<__nv_bfloat16><<<n, threads, 0, s>>>(ids, (const __nv_bfloat16*)table,
+                                                               out, width, vocab);
+    else
+        embed_rows_kernel<float><<<n, threads, 0, s>>>(ids, (const float*)table, out, width, vocab);
+    return de_check(cudaGetLastError());
+}
+
+// ------------------------------------------------------------------------------------------
+// residual sum + RMS norm.
+//   x = resid[row] (+ delta[row]);  resid[row] = x (when update);  var = mean(x^2)
+//   y = T(x * rsqrt(var + eps));    out[i] = T(float(y) * float(weight))
+// The cast to the activation type comes before the multiplication by the weight, as in
+// src/layers/layernorm.py:21-23.  `rows` (may be null) picks the rows to normalise: out[i] comes
+// from row rows[i], and resid is then left as it is.
+// ------------------------------------------------------------------------------------------
+template <typename T, typename W>
+__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restrict__ delta,
+                                   const W* __restrict__ weight, T* __restrict__ out,
+                                   const int* __restrict__ rows, int width, float eps) {
+    __shared__ float scratch[33];
+    const int i_out = blockIdx.x;
+    const int row = rows ? rows[i_out] : i_out;
+    float* r = resid + (size_t)row * width;
+    const T* d = delta ? delta + (size_t)row * width : nullptr;
+    const bool update = (rows == nullptr) && (delta != nullptr);
+
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float x = r[i];
+        if (d) x += to_float(d[i]);
+        if (update) r[i] = x;
+        ss += x * x;
+    }
+    const float total = block_sum(ss, scratch);
+    const float inv = rsqrtf(total / (float)width + eps);
+    T* o = out + (size_t)i_out * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float x = r[i];
+        if (d && !update) x += to_float(d[i]);       // same sum as above, bit for bit
+        const float y = to_float(from_float<T>(x * inv));
+        o[i] = from_float<T>(y * to_float(weight[i]));
+    }
+}
+
+DE_EXPORT int de_add_rmsnorm(int dtype, int weight_dtype, float* resid, const void* delta,
+                             const void* weight, void* out, const int* rows, int n_out, int width,
+                             float eps, void* stream) {
+    if (n_out <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+#define LAUNCH(T, W)                                                                        \
+    add_rmsnorm_kernel<T, W><<<n_out, threads, 0, s>>>(resid, (const T*)delta, (const W*)weight, \
+                                                       (T*)out, rows, width, eps)
+    if (dtype == DE_BF16) {
+        if (weight_dtype == DE_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+        else LAUNCH(__nv_bfloat16, float);
+    } else {
+        if (weight_dtype == DE_BF16) LAUNCH(float, __nv_bfloat16);
+        else LAUNCH(float, float);
+    }
+#undef LAUNCH
+    return de_check(cudaGetLastError());
+}
+
+// ------------------------------------------------------------------------------------------
+// rotation of q and k by position + write of k and v into the pages of the cache.
+//   qkv row = [q heads | k heads | v heads], each head `d` wide.
+//   pair (j, j + rot/2) of a head is rotated by angle = float(pos) * inv_freq[j]
+//   (half-split pairing, src/layers/rotary_embedding.py:45-54); dims >= rot stay.
+//   q is rotated in place; rotated k and v go to
+//   pages[(block_table[slot][pos / page] * kv_heads + h) * page + pos % page][:]
+//   (position -> page and offset as in src/distengine/paged_kv_cache.py:165-167).
+// inv_freq null: no rotation.  write_kv 0: a layer that reads another layer's cache rotates q only.
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride,
+                                     const int* __restrict__ positions,
+                                     const int* __restrict__ token_slot,
+                                     const float* __restrict__ inv_freq, int rot, int heads,
+                                     int kv_heads, int d, T* __restrict__ k_pages,
+                                     T* __restrict__ v_pages, const int* __restrict__ block_table,
+                                     int table_stride, int page, int write_kv, int num_pages,
+                                     int* __restrict__ status) {
+    const int n = blockIdx.x;
+    const int pos = positions[n];
+    T* row = qkv + (size_t)n * row_stride;
+    const int half = rot / 2;
+
+    size_t kv_base = 0;
+    bool can_write = write_kv != 0;
+    if (can_write) {
+        const int slot = token_slot[n];
+        const int page_id = block_table[(size_t)slot * table_stride + pos / page];
+        if (page_id < 0 || page_id >= num_pages) {      // a table without a page here: record, skip
+            if (threadIdx.x == 0 && threadIdx.y == 0) atomicExch(status, 1);
+            can_write = false;
+        }
+        kv_base = ((size_t)page_id * kv_heads) * page * d + (size_t)(pos % page) * d;
+    }
+    const size_t head_step = (size_t)page * d;          // from one kv head's slab to the next
+
+    // rotated pairs: threadIdx.x walks the pair index, threadIdx.y the heads
+    for (int j = threadIdx.x; j < half; j += blockDim.x) {
+        float c = 1.0f, s = 0.0f;
+        if (inv_freq) {
+            const float angle = (float)pos * inv_freq[j];
+            c = cosf(angle);
+            s = sinf(angle);
+        }
+        for (int h = threadIdx.y; h < heads + kv_heads; h += blockDim.y) {
+            T* x = row + (size_t)h * d;
+            const float a = to_float(x[j]), b = to_float(x[j + half]);
+            const T ra = from_float<T>(a * c - b * s);
+            const T rb = from_float<T>(b * c + a * s);
+            if (h < heads) {
+                x[j] = ra;
+                x[j + half] = rb;
+            } else if (can_write) {
+                T* dst = k_pages + kv_base + (size_t)(h - heads) * head_step;
+                dst[j] = ra;
+                dst[j + half] = rb;
+            }
+        }
+    }
+    if (!can_write) return;
+    // k dims beyond the rotated width are copied as they are
+    for (int j = rot + threadIdx.x; j < d; j += blockDim.x)
+        for (int h = threadIdx.y; h < kv_heads; h += blockDim.y)
+            k_pages[kv_base + (size_t)h * head_step + j] = row[(size_t)(heads + h) * d + j];
+    // v
+    for (int j = threadIdx.x; j < d; j += blockDim.x)
+        for (int h = threadIdx.y; h < kv_heads; h += blockDim.y)
+            v_pages[kv_base + (size_t)h * head_step + j] =
+                row[(size_t)(heads + kv_heads + h) * d + j];
+}
+
+DE_EXPORT int de_rope_kv_write(int dtype, void* qkv, int row_stride, const int* positions,
+                               const int* token_slot, const float* inv_freq, int rot, int heads,
+                               int kv_heads, int d, void* k_pages, void* v_pages,
+                               const int* block_table, int table_stride, int page, int write_kv,
+                               int num_pages, int n, int* status, void* stream) {
+    if (n <= 0) return 0;
+    if (rot < 0 || rot > d || (rot & 1)) return -2;
+    cudaStream_t s = (cudaStream_t)stream;
+    int tx = 32;
+    while (tx < d / 2 && tx < 128) tx <<= 1;
+    int ty = 256 / tx;
+    dim3 block(tx, ty);
+#define LAUNCH(T)                                                                              \
+    rope_kv_write_kernel<T><<<n, block, 0, s>>>((T*)qkv, row_stride, positions, token_slot,    \
+                                                inv_freq, rot, heads, kv_heads, d, (T*)k_pages, \
+                                                (T*)v_pages, block_table, table_stride, page,  \
+                                                write_kv, num_pages, status)
+    if (dtype == DE_BF16) LAUNCH(__nv_bfloat16);
+    else LAUNCH(float);
+#undef LAUNCH
+    return de_check(cudaGetLastError());
+}
+
+// ------------------------------------------------------------------------------------------
+// out[n, i] = T( silu(gate) * up ), gate = x[n, i], up = x[n, inner + i]; silu(z) = z * sigmoid(z)
+// (src/layers/activation.py:6-9; the packed [gate | up] row as in src/models/llama.py:26).
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ x, T* __restrict__ out, int inner,
+                                size_t total) {
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t n = idx / inner;
+        const int i = (int)(idx - n * inner);
+        const float g = to_float(x[n * 2 * inner + i]);
+        const float u = to_float(x[n * 2 * inner + inner + i]);
+        const float sg = g / (1.0f + expf(-g));
+        out[idx] = from_float<T>(sg * u);
+    }
+}
+
+DE_EXPORT int de_silu_mul(int dtype, const void* x, void* out, int n, int inner, void* stream) {
+    if (n <= 0) return 0;
+    const size_t total = (size_t)n * inner;
+    const int threads = 256;
+    size_t blocks = (total + threads - 1) / threads;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == DE_BF16)
+        silu_mul_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, s>>>(
+            (const __nv_bfloat16*)x, (__nv_bfloat16*)out, inner, total);
+    else
+        silu_mul_kernel<float><<<(int)blocks, threads, 0, s>>>((const float*)x, (float*)out, inner,
+                                                              total);
+    return de_check(cudaGetLastError());
+}
+
+// ------------------------------------------------------------------------------------------
+// sampling over rows of float32 logits.
+//   temperature 0: arg-max, the lowest id wins a tie (src/layers/sampler.py:8).
+//   temperature > 0: a draw from softmax(logits / T) by the Gumbel-max rule,
+//     arg-max_i( logits_i / T - log(-log(u_i)) ),  u_i a counter-based uniform of
+//     (seed, position, i): the draw depends on the request's own seed and position only, never on
+//     the batch.  The reference samples greedily only.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ float uniform_of(unsigned long long base, int i) {
+    unsigned long long z = base + (unsigned long long)(i + 1) * 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z = z ^ (z >> 31);
+    return ((float)(z >> 41) + 0.5f) * (1.0f / 8388608.0f);     // 23 bits + 0.5: exact, in (0,1)
+}
+
+__global__ void sample_rows_kernel(const float* __restrict__ logits, int vocab,
+                                   const float* __restrict__ temperature,
+                                   const long long* __restrict__ seed,
+                                   const int* __restrict__ position, int* __restrict__ out) {
+    __shared__ float best_v[32];
+    __shared__ int best_i[32];
+    const int r = blockIdx.x;
+    const float* row = logits + (size_t)r * vocab;
+    const float t = temperature ? temperature[r] : 0.0f;
+    unsigned long long base = 0;
+    if (t > 0.0f)
+        base = (unsigned long long)seed[r] * 0x9E3779B97F4A7C15ull +
+               (unsigned long long)(long long)position[r] * 0xD1B54A32D192ED03ull;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        float v = row[i];
+        if (t > 0.0f) v = v / t - logf(-logf(uniform_of(base, i)));
+        if (v > bv || (v == bv && i < bi) || bi == 0x7fffffff) { bv = v; bi = i; }
+    }
+    // reduce (value, lowest index on ties) over the block
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) {
+            bv = ov; bi = oi;
+        }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { best_v[warp] = bv; best_i[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+        const int warps = (blockDim.x + 31) >> 5;
+        bv = lane < warps ? best_v[lane] : -INFINITY;
+        bi = lane < warps ? best_i[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) {
+                bv = ov; bi = oi;
+            }
+        }
+        if (lane == 0) out[r] = bi == 0x7fffffff ? 0 : bi;
+    }
+}
+
+DE_EXPORT int de_sample_rows(const float* logits, int rows, int vocab, const float* temperature,
+                             const long long* seed, const int* position, int* out, void* stream) {
+    if (rows <= 0) return 0;
+    sample_rows_kernel<<<rows, 1024, 0, (cudaStream_t)stream>>>(logits, vocab, temperature, seed,
+                                                                position, out);
+    return de_check(cudaGetLastError());
+}

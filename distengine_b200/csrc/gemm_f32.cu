@@ -1,0 +1,107 @@
+// True 32-bit matrix product for the float32 path: out[n, m] = sum_k x[n, k] * w[m, k].
+// IEEE float32 multiply-adds on the CUDA cores: no tensor cores, no TF32, no reduced-precision
+// staging.  Every output element is one chain of fused multiply-adds over k = 0, 1, ... K-1 in
+// that order, whatever the number of rows, so a row's result does not depend on the batch it is in.
+//
+// It stands where the reference calls F.linear in float32 with TF32 switched off
+// (src/layers/linear.py:19-20, src/distengine/worker.py:427-428).
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 64;   // rows of x per block
+constexpr int BN = 64;   // rows of w (output features) per block
+constexpr int BK = 16;
+
+template <bool VEC4>
+__global__ void __launch_bounds__(256)
+gemm_f32_kernel(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ out,
+                int n_rows, int m_cols, int k_dim, int ldx, int ldw, int ldo) {
+    __shared__ float xs[BK][BM + 4];
+    __shared__ float ws[BK][BN + 4];
+
+    const int tid = threadIdx.x;
+    const int ty = tid / 16, tx = tid % 16;
+    const int row0 = blockIdx.y * BM, col0 = blockIdx.x * BN;
+
+    // each thread stages 4 consecutive k of one row of each tile
+    const int l_row = tid / 4, l_k = (tid % 4) * 4;
+
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+
+    for (int k0 = 0; k0 < k_dim; k0 += BK) {
+        float xv[4] = {0.f, 0.f, 0.f, 0.f}, wv[4] = {0.f, 0.f, 0.f, 0.f};
+        const int gr = row0 + l_row, gc = col0 + l_row, gk = k0 + l_k;
+        if (gr < n_rows) {
+            const float* p = x + (size_t)gr * ldx + gk;
+            if (VEC4 && gk + 3 < k_dim) {
+                const float4 t = *reinterpret_cast<const float4*>(p);
+                xv[0] = t.x; xv[1] = t.y; xv[2] = t.z; xv[3] = t.w;
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) if (gk + i < k_dim) xv[i] = p[i];
+            }
+        }
+        if (gc < m_cols) {
+            const float* p = w + (size_t)gc * ldw + gk;
+            if (VEC4 && gk + 3 < k_dim) {
+                const float4 t = *reinterpret_cast<const float4*>(p);
+                wv[0] = t.x; wv[1] = t.y; wv[2] = t.z; wv[3] = t.w;
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) if (gk + i < k_dim) wv[i] = p[i];
+            }
+        }
+        __syncthreads();                       // the previous tile has been consumed
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            xs[l_k + i][l_row] = xv[i];
+            ws[l_k + i][l_row] = wv[i];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < BK; ++k) {
+            const float4 a = *reinterpret_cast<const float4*>(&xs[k][ty * 4]);
+            const float4 b = *reinterpret_cast<const float4*>(&ws[k][tx * 4]);
+            const float av[4] = {a.x, a.y, a.z, a.w};
+            const float bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = row0 + ty * 4 + i;
+        if (r >= n_rows) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int c = col0 + tx * 4 + j;
+            if (c < m_cols) out[(size_t)r * ldo + c] = acc[i][j];
+        }
+    }
+}
+
+}  // namespace
+
+DE_EXPORT int de_gemm_f32(const float* x, const float* w, float* out, int n_rows, int m_cols,
+                          int k_dim, int ldx, int ldw, int ldo, void* stream) {
+    if (n_rows <= 0 || m_cols <= 0) return 0;
+    if (k_dim <= 0) return -2;
+    dim3 grid((m_cols + BN - 1) / BN, (n_rows + BM - 1) / BM);
+    if (grid.y > 65535) return -3;
+    cudaStream_t s = (cudaStream_t)stream;
+    const bool vec = (ldx % 4 == 0) && (ldw % 4 == 0) && (((uintptr_t)x) % 16 == 0) &&
+                     (((uintptr_t)w) % 16 == 0);
+    if (vec)
+        gemm_f32_kernel<true><<<grid, 256, 0, s>>>(x, w, out, n_rows, m_cols, k_dim, ldx, ldw, ldo);
+    else
+        gemm_f32_kernel<false><<<grid, 256, 0, s>>>(x, w, out, n_rows, m_cols, k_dim, ldx, ldw, ldo);
+    return de_check(cudaGetLastError());
+}

@@ -1,0 +1,110 @@
+"""Cuts a step's attention into work items on the host.
+
+A work item is a tile of query rows of one sequence (rows are (token, query head within its kv
+head's group), token-major) together with a range of key positions.  Prompt portions get one item
+per tile, covering all keys up to the tile's last position.  When a step has too few tiles to fill
+the GPU (decoded tokens over long contexts), a tile's key range is cut into chunks at absolute
+multiples of ``chunk``; each chunk writes a partial result and a combine item names the chunks of
+the tile.  The layout of an item matches ``struct WorkItem`` / ``CombineItem`` in the kernels.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+
+SM_COUNT = 148
+CHUNKS = (2048, 1024, 512, 256, 128, 64)
+
+
+@dataclass
+class AttentionPlan:
+    items: np.ndarray          # int32 [num_items, 8]
+    combine: np.ndarray        # int32 [num_combine, 4]
+    num_partials: int          # partial slots used (each: kv_heads x rows_per_tile rows)
+    rows_per_tile: int
+    chunk: int                 # 0: nothing is split
+
+
+def _tiles(seq_qlen: np.ndarray, seq_pos0: np.ndarray, group: int, rows_per_tile: int,
+           window: int):
+    """(seq, row0, lo, hi) of every tile, vectorised over sequences."""
+    rows_total = seq_qlen.astype(np.int64) * group
+    tiles_per_seq = (rows_total + rows_per_tile - 1) // rows_per_tile
+    total = int(tiles_per_seq.sum())
+    seq = np.repeat(np.arange(len(seq_qlen), dtype=np.int64), tiles_per_seq)
+    first = np.cumsum(tiles_per_seq) - tiles_per_seq
+    row0 = (np.arange(total, dtype=np.int64) - np.repeat(first, tiles_per_seq)) * rows_per_tile
+    last_row = np.minimum(row0 + rows_per_tile, rows_total[seq]) - 1
+    pos0 = seq_pos0.astype(np.int64)[seq]
+    hi = pos0 + last_row // group + 1
+    if window > 0:
+        lo = np.maximum(0, pos0 + row0 // group - window + 1)
+    else:
+        lo = np.zeros(total, dtype=np.int64)
+    return seq, row0, lo, hi
+
+
+def choose_chunk(num_tiles: int, kv_heads: int, longest: int) -> int:
+    """The largest chunk that still gives every SM about two blocks; 0: do not split."""
+    if num_tiles * kv_heads >= 2 * SM_COUNT:
+        return 0
+    for chunk in CHUNKS:
+        if num_tiles * kv_heads * ((longest + chunk - 1) // chunk) >= 2 * SM_COUNT:
+            return chunk
+    return CHUNKS[-1]
+
+
+def build_plan(seq_qlen: np.ndarray, seq_pos0: np.ndarray, group: int, kv_heads: int,
+               rows_per_tile: int, window: int = 0, chunk: "int | None" = None,
+               chunks_cap: "int | None" = None) -> AttentionPlan:
+    """``chunk`` None: chosen from the step's shape.  ``chunks_cap`` (with a given chunk): every
+    tile gets exactly that many items and one combine item, padded with empty ones, so that the
+    arrays' shapes depend on the number of tiles only (what a replayed CUDA graph needs)."""
+    seq, row0, lo, hi = _tiles(seq_qlen, seq_pos0, group, rows_per_tile, window)
+    total = len(seq)
+    if chunk is None:
+        longest = int((hi - lo).max()) if total else 0
+        chunk = choose_chunk(total, kv_heads, longest)
+    if chunk == 0 or total == 0:
+        items = np.zeros((total, 8), dtype=np.int32)
+        items[:, 0], items[:, 1], items[:, 2], items[:, 3], items[:, 4] = seq, row0, 0, hi, -1
+        return AttentionPlan(items, np.zeros((0, 4), dtype=np.int32), 0, rows_per_tile, 0)
+
+    c0 = lo // chunk
+    c1 = (hi - 1) // chunk
+    count = c1 - c0 + 1
+    if chunks_cap is None:
+        split = count > 1
+        n_items = np.where(split, count, 1)
+    else:
+        if int(count.max()) > chunks_cap:
+            raise ValueError(f"a key range needs {int(count.max())} chunks of {chunk}, the plan "
+                             f"was capped at {chunks_cap}")
+        split = np.ones(total, dtype=bool)
+        n_items = np.full(total, chunks_cap, dtype=np.int64)
+    item_first = np.cumsum(n_items) - n_items
+    num_items = int(n_items.sum())
+    owner = np.repeat(np.arange(total, dtype=np.int64), n_items)
+    k = np.arange(num_items, dtype=np.int64) - item_first[owner]        # chunk index within tile
+    c = c0[owner] + k
+    begin = np.where(split[owner], c * chunk, 0)
+    end = np.where(split[owner], np.minimum(hi[owner], (c + 1) * chunk), hi[owner])
+    live = k < count[owner]
+    begin = np.where(live, begin, 0)
+    end = np.where(live, end, 0)
+
+    # partial slots: consecutive for the chunks of one tile
+    n_part = np.where(split, n_items, 0)
+    part_first = np.cumsum(n_part) - n_part
+    partial = np.where(split[owner], part_first[owner] + k, -1)
+
+    items = np.zeros((num_items, 8), dtype=np.int32)
+    items[:, 0], items[:, 1], items[:, 2], items[:, 3], items[:, 4] = (
+        seq[owner], row0[owner], begin, end, partial)
+    sel = np.nonzero(split)[0]
+    combine = np.zeros((len(sel), 4), dtype=np.int32)
+    combine[:, 0], combine[:, 1], combine[:, 2] = seq[sel], row0[sel], part_first[sel]
+    combine[:, 3] = count[sel]
+    return AttentionPlan(items, combine, int(n_part.sum()), rows_per_tile, chunk)

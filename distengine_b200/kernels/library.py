@@ -1,0 +1,77 @@
+"""Loads the compiled kernel libraries and declares their C signatures.
+
+There is no fallback: if a library cannot be compiled or loaded, or no CUDA device is present, the
+first kernel call raises ``KernelsUnavailable`` with the reason.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+
+from . import build as _build
+
+
+class KernelsUnavailable(RuntimeError):
+    pass
+
+
+P, I, F = c_void_p, c_int, c_float
+
+# module -> {function: argument types}; every function returns an int (0, or a CUDA error code,
+# or a negative number for arguments the kernel refuses)
+SIGNATURES: dict[str, dict[str, list]] = {
+    "core": {
+        "de_embed_rows": [I, P, P, P, I, I, I, P],
+        "de_add_rmsnorm": [I, I, P, P, P, P, P, I, I, F, P],
+        "de_rope_kv_write": [I, P, I, P, P, P, I, I, I, I, P, P, P, I, I, I, I, I, P, P],
+        "de_silu_mul": [I, P, P, I, I, P],
+        "de_sample_rows": [P, I, I, P, P, P, P, P],
+    },
+    "gemm_f32": {
+        "de_gemm_f32": [P, P, P, I, I, I, I, I, I, P],
+    },
+    "attention_simt": {
+        "de_attn_simt_rows_per_tile": [],
+        "de_attn_simt": [I, P, I, P, I, P, P, P, I, I, P, P, P, P, P, I, P, P, I, I, I, I, F, I, P],
+        "de_attn_combine": [I, P, I, P, P, P, I, P, P, I, I, I, I, P],
+    },
+}
+
+_loaded: dict[tuple[str, tuple[str, ...]], ctypes.CDLL] = {}
+
+
+def default_build_requests() -> list[tuple[str, tuple[str, ...]]]:
+    return [(module, ()) for module in _build.MODULES if module in SIGNATURES]
+
+
+def load(module: str, defines: tuple[str, ...] = ()) -> ctypes.CDLL:
+    key = (module, defines)
+    lib = _loaded.get(key)
+    if lib is not None:
+        return lib
+    try:
+        path = _build.build(module, defines)
+        lib = ctypes.CDLL(path)
+    except (_build.BuildError, OSError) as error:
+        raise KernelsUnavailable(
+            f"the CUDA kernel library '{module}' of distengine_b200 could not be built or "
+            f"loaded: {error}") from error
+    for name, argtypes in SIGNATURES[module].items():
+        fn = getattr(lib, name)
+        fn.argtypes = argtypes
+        fn.restype = c_int
+    _loaded[key] = lib
+    return lib
+
+
+def preload(modules: list[tuple[str, tuple[str, ...]]]) -> None:
+    """Compile several modules side by side, then load them."""
+    missing = [m for m in modules if m not in _loaded]
+    if missing:
+        try:
+            _build.build_many(missing)
+        except _build.BuildError as error:
+            raise KernelsUnavailable(str(error)) from error
+    for module, defines in modules:
+        load(module, defines)

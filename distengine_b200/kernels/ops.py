@@ -1,0 +1,195 @@
+"""The kernels as functions of torch tensors.  Every function launches on the current CUDA stream
+and checks shapes, dtypes and strides before it passes pointers on; a size that a kernel does not
+take is refused with an error that names it.  Nothing here falls back to the CPU or to library
+model code.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import library
+from .library import KernelsUnavailable
+
+F32, BF16 = 0, 1
+
+# how many kernels of this package were launched (bench.py reports it)
+launch_count = 0
+
+
+def _tag(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise TypeError(f"kernels take float32 or bfloat16 tensors, got {dtype}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: "torch.Tensor | None") -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _check(code: int, what: str) -> None:
+    global launch_count
+    launch_count += 1
+    if code == 0:
+        return
+    if code < 0:
+        raise ValueError(f"{what}: the kernel refuses these sizes (code {code})")
+    raise RuntimeError(f"{what}: CUDA error {code} at launch")
+
+
+def _need(cond: bool, message: str) -> None:
+    if not cond:
+        raise ValueError(message)
+
+
+def require_device(device: "torch.device | str") -> torch.device:
+    """The CUDA device to run on; raises if there is none."""
+    device = torch.device(device)
+    if device.type != "cuda":
+        raise KernelsUnavailable(f"distengine_b200 runs on a CUDA device only, got '{device}'")
+    if not torch.cuda.is_available():
+        raise KernelsUnavailable("distengine_b200 needs a CUDA device (sm_100a) and none is "
+                                 "visible; there is no CPU path")
+    return device
+
+
+def _i32(t: torch.Tensor, name: str) -> None:
+    _need(t.dtype == torch.int32 and t.is_contiguous() and t.is_cuda,
+          f"{name} must be a contiguous int32 CUDA tensor")
+
+
+# ------------------------------------------------------------------------------- embedding
+def embed_rows(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
+    """out[n] = float32(table[ids[n]]); ids int32 [N], table [V, H], out float32 [N, H]."""
+    _i32(ids, "ids")
+    n, (vocab, width) = ids.shape[0], table.shape
+    _need(table.is_contiguous() and out.is_contiguous() and out.dtype == torch.float32
+          and tuple(out.shape) == (n, width), "embed_rows: out must be float32 [N, H]")
+    lib = library.load("core")
+    _check(lib.de_embed_rows(_tag(table.dtype), ids.data_ptr(), table.data_ptr(), out.data_ptr(),
+                             n, width, vocab, _stream()), "embed_rows")
+
+
+# ------------------------------------------------------------------------------- norm
+def add_rmsnorm(resid: torch.Tensor, delta: "torch.Tensor | None", weight: torch.Tensor,
+                eps: float, out: torch.Tensor, rows: "torch.Tensor | None" = None) -> None:
+    """out = rmsnorm(resid + delta) * weight; resid (float32) takes the sum unless ``rows`` picks
+    the rows to normalise (then out[i] comes from row rows[i] and resid is not written)."""
+    width = resid.shape[1]
+    n_out = resid.shape[0] if rows is None else rows.shape[0]
+    _need(resid.dtype == torch.float32 and resid.is_contiguous(), "resid must be float32")
+    _need(out.is_contiguous() and tuple(out.shape) == (n_out, width), "add_rmsnorm: out shape")
+    _need(weight.is_contiguous() and weight.shape == (width,), "add_rmsnorm: weight shape")
+    if delta is not None:
+        _need(delta.dtype == out.dtype and delta.is_contiguous()
+              and delta.shape == resid.shape, "add_rmsnorm: delta must match resid's shape and "
+              "the output's dtype")
+    if rows is not None:
+        _i32(rows, "rows")
+    lib = library.load("core")
+    _check(lib.de_add_rmsnorm(_tag(out.dtype), _tag(weight.dtype), resid.data_ptr(), _ptr(delta),
+                              weight.data_ptr(), out.data_ptr(), _ptr(rows), n_out, width,
+                              float(eps), _stream()), "add_rmsnorm")
+
+
+# ------------------------------------------------------------------------------- rotation + cache write
+def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, token_slot: torch.Tensor,
+                  inv_freq: "torch.Tensor | None", rotary_dim: int, heads: int, kv_heads: int,
+                  head_dim: int, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                  block_table: torch.Tensor, write_kv: bool, status: torch.Tensor) -> None:
+    """Rotate q and k of qkv [N, (heads + 2 kv_heads) * d] in place by position and store k, v in
+    the pages [pages, kv_heads, page, d] through block_table [slots, max_pages]."""
+    n = qkv.shape[0]
+    _need(qkv.stride(1) == 1 and qkv.shape[1] == (heads + 2 * kv_heads) * head_dim,
+          "rope_kv_write: qkv must be [N, (heads + 2 kv_heads) * head_dim]")
+    _i32(positions, "positions"), _i32(token_slot, "token_slot"), _i32(block_table, "block_table")
+    _i32(status, "status")
+    _need(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.shape == v_pages.shape
+          and k_pages.dtype == qkv.dtype == v_pages.dtype and k_pages.dim() == 4
+          and k_pages.shape[1] == kv_heads and k_pages.shape[3] == head_dim,
+          "rope_kv_write: pages must be [pages, kv_heads, page, head_dim] of qkv's dtype")
+    _need(rotary_dim % 2 == 0 and 0 <= rotary_dim <= head_dim,
+          f"rope_kv_write: rotary_dim {rotary_dim} must be even and at most head_dim {head_dim}")
+    if inv_freq is not None:
+        _need(inv_freq.dtype == torch.float32 and inv_freq.is_contiguous()
+              and inv_freq.shape == (rotary_dim // 2,), "rope_kv_write: inv_freq shape")
+    lib = library.load("core")
+    _check(lib.de_rope_kv_write(_tag(qkv.dtype), qkv.data_ptr(), qkv.stride(0),
+                                positions.data_ptr(), token_slot.data_ptr(), _ptr(inv_freq),
+                                rotary_dim, heads, kv_heads, head_dim, k_pages.data_ptr(),
+                                v_pages.data_ptr(), block_table.data_ptr(), block_table.stride(0),
+                                k_pages.shape[2], int(write_kv), k_pages.shape[0], n,
+                                status.data_ptr(), _stream()), "rope_kv_write")
+
+
+# ------------------------------------------------------------------------------- feed-forward
+def silu_mul(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out[n, i] = silu(x[n, i]) * x[n, inner + i]; x [N, 2 inner], out [N, inner]."""
+    n, inner = out.shape
+    _need(x.is_contiguous() and out.is_contiguous() and x.shape == (n, 2 * inner)
+          and x.dtype == out.dtype, "silu_mul: x must be [N, 2 inner] and out [N, inner]")
+    lib = library.load("core")
+    _check(lib.de_silu_mul(_tag(x.dtype), x.data_ptr(), out.data_ptr(), n, inner, _stream()),
+           "silu_mul")
+
+
+# ------------------------------------------------------------------------------- matrix products
+def gemm_f32(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[n, m] = sum_k x[n, k] w[m, k] in IEEE float32 on the CUDA cores."""
+    _need(x.dtype == w.dtype == out.dtype == torch.float32, "gemm_f32 takes float32 tensors")
+    _need(x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1]
+          and tuple(out.shape) == (x.shape[0], w.shape[0]), "gemm_f32: shapes do not agree")
+    _need(x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1,
+          "gemm_f32: rows must be contiguous")
+    lib = library.load("gemm_f32")
+    _check(lib.de_gemm_f32(x.data_ptr(), w.data_ptr(), out.data_ptr(), x.shape[0], w.shape[0],
+                           x.shape[1], x.stride(0), w.stride(0), out.stride(0), _stream()),
+           "gemm_f32")
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out: "torch.Tensor | None" = None,
+           out_dtype: "torch.dtype | None" = None) -> torch.Tensor:
+    """x @ w^T.  float32: this package's own kernel (true 32-bit).  bfloat16: the library matrix
+    product (cuBLAS through torch), where the reference calls a library too
+    (src/layers/linear.py:19-20); float32 accumulation, output bfloat16 or float32."""
+    out_dtype = out_dtype or x.dtype
+    if out is None:
+        out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=x.device)
+    if x.shape[0] == 0:
+        return out
+    if x.dtype == torch.float32:
+        _need(out.dtype == torch.float32, "linear: a float32 product has a float32 output")
+        gemm_f32(x, w, out)
+        return out
+    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16,
+          "linear: operands must both be bfloat16 or both float32")
+    if out.dtype == torch.bfloat16:
+        torch.mm(x, w.t(), out=out)
+    else:
+        torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
+    return out
+
+
+# ------------------------------------------------------------------------------- sampling
+def sample_rows(logits: torch.Tensor, out: torch.Tensor,
+                temperature: "torch.Tensor | None" = None, seed: "torch.Tensor | None" = None,
+                position: "torch.Tensor | None" = None) -> None:
+    """out[r] = arg-max of row r (temperature null or 0) or a seeded draw from
+    softmax(logits / temperature)."""
+    rows, vocab = logits.shape
+    _need(logits.dtype == torch.float32 and logits.is_contiguous(), "logits must be float32")
+    _i32(out, "out")
+    if temperature is not None:
+        _need(temperature.dtype == torch.float32 and seed is not None and position is not None
+              and seed.dtype == torch.int64 and position.dtype == torch.int32
+              and temperature.shape[0] == seed.shape[0] == position.shape[0] == rows,
+              "sample_rows: temperature float32, seed int64, position int32, one per row")
+    lib = library.load("core")
+    _check(lib.de_sample_rows(logits.data_ptr(), rows, vocab, _ptr(temperature), _ptr(seed),
+                              _ptr(position), out.data_ptr(), _stream()), "sample_rows")

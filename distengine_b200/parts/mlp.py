@@ -1,0 +1,46 @@
+"""Dense gated feed-forward (SwiGLU): down( silu(gate(x)) * up(x) ), no biases
+(src/models/llama.py:13-29, src/layers/activation.py:6-9).  gate and up are one product against
+the stacked matrix [2 inner, width]; the reference runs two and concatenates (llama.py:23-26).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from .base import FeedForward, compute_matrix, register_feed_forward
+from .context import StepContext
+
+
+class GatedMLP(FeedForward):
+    def __init__(self, width: int, inner: int, activation: str, dtype: torch.dtype,
+                 device: torch.device) -> None:
+        super().__init__(dtype, device)
+        if activation != "silu":
+            raise ValueError(f"gated_mlp: activation '{activation}' is not implemented; 'silu' is")
+        self.width, self.inner = width, inner
+        self.w_gate_up: "torch.Tensor | None" = None
+        self.w_down: "torch.Tensor | None" = None
+
+    def tensors(self):
+        return {"gate_proj.weight": ((self.inner, self.width), "matrix"),
+                "up_proj.weight": ((self.inner, self.width), "matrix"),
+                "down_proj.weight": ((self.width, self.inner), "matrix")}
+
+    def load(self, tensors):
+        stacked = torch.cat((tensors["gate_proj.weight"], tensors["up_proj.weight"]), dim=0)
+        self.w_gate_up = compute_matrix(stacked, self.dtype, self.device)
+        self.w_down = compute_matrix(tensors["down_proj.weight"], self.dtype, self.device)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        n = x.shape[0]
+        gate_up = ctx.buffer("mlp.gate_up", (n, 2 * self.inner))
+        ops.linear(x, self.w_gate_up, out=gate_up)
+        act = ctx.buffer("mlp.act", (n, self.inner))
+        ops.silu_mul(gate_up, act)
+        out = ctx.buffer("mlp.out", (n, self.width))
+        ops.linear(act, self.w_down, out=out)
+        return out
+
+
+register_feed_forward("gated_mlp", GatedMLP)

@@ -1,0 +1,39 @@
+"""RMS norm with the residual sum folded in.
+
+Formula (src/layers/layernorm.py:12-23): float32 mean of squares, x * rsqrt(mean + eps), cast to
+the activation dtype, then times the weight.  The block's residual sums
+(src/models/llama.py:74-89) happen in the same kernel, in 32-bit.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from .base import Norm, register_norm, stored_vector
+from .context import ResidualStream, StepContext
+
+
+class RMSNorm(Norm):
+    def __init__(self, width: int, eps: float, dtype: torch.dtype, device: torch.device) -> None:
+        super().__init__(dtype, device)
+        self.width, self.eps = width, eps
+        self.weight: "torch.Tensor | None" = None
+
+    def tensors(self):
+        return {"weight": ((self.width,), "vector")}
+
+    def load(self, tensors):
+        self.weight = stored_vector(tensors["weight"], self.dtype, self.device)
+
+    def forward(self, stream: ResidualStream, ctx: StepContext, rows=None,
+                out_name: str = "norm.out") -> torch.Tensor:
+        n_out = stream.resid.shape[0] if rows is None else rows.shape[0]
+        out = ctx.buffer(out_name, (n_out, self.width))
+        ops.add_rmsnorm(stream.resid, stream.pending, self.weight, self.eps, out, rows)
+        if rows is None:
+            stream.pending = None              # it is part of the residual now
+        return out
+
+
+register_norm("rmsnorm", RMSNorm)
