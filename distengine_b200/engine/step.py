@@ -1,0 +1,174 @@
+"""The step function: one batch of (request, its next tokens) through the model, from the cache.
+
+A step holds prompt portions of any length beside single decoded tokens, cut anywhere.  It runs
+only the tokens it is given, as one ragged batch, against the keys and values that earlier steps
+left in the pages, and returns float32 logits at the wanted places.  It samples nothing and keeps
+no request state beyond the cache's lengths; the scheduler and the trace replay both drive it.
+
+The reference's nearest relative is ``ModelRunner`` (src/distengine/model_runner.py): ``prefill``
+runs one whole prompt (:113-173), ``decode_batch`` runs B single tokens (:226-269); a batch there
+is never mixed and a prompt never cut.  Kept from it: tokens are validated against the vocabulary
+(:72-77), positions continue from the cache's length (src/models/llama.py:177-179), pages for the
+whole batch are taken before anything is written or the step does not start (:244-256), and all
+per-step index arrays are built once on the host and reused by every layer
+(src/distengine/paged_kv_cache.py:263-293).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from types import SimpleNamespace
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager
+from ..kernels import ops
+from ..parts.context import StepContext, StepPrep, Workspace
+
+
+@dataclass
+class StepEntry:
+    request_id: str
+    tokens: list[int]
+    want: list[int] = field(default_factory=list)      # places among ``tokens``
+
+
+class KernelStatusError(RuntimeError):
+    """A kernel found an index it could not use (a position without a page) and skipped work."""
+
+
+def _align(n: int) -> int:
+    return (n + 3) & ~3
+
+
+class StepRunner:
+    def __init__(self, model, cache: CacheManager, use_graphs: bool = False) -> None:
+        self.model, self.cache = model, cache
+        self.device, self.dtype = model.device, model.dtype
+        ops.require_device(self.device)
+        self.vocabulary = model.config.vocabulary
+        self.workspace = Workspace(self.device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._host_meta: "torch.Tensor | None" = None        # pinned int32 staging
+        self._dev_meta: "torch.Tensor | None" = None
+        self._uploaded = torch.cuda.Event()
+        self._upload_pending = False
+        self.bindings = cache.bindings()
+        self.use_graphs = use_graphs
+        self.steps_run = 0
+
+    # ------------------------------------------------------------------ host side
+    def _validate(self, entries: list[StepEntry]) -> None:
+        if not entries:
+            raise ValueError("a step needs at least one entry")
+        seen = set()
+        for e in entries:
+            if not isinstance(e.request_id, str) or not e.request_id:
+                raise ValueError("request_id must be a nonempty string")
+            if e.request_id in seen:
+                raise ValueError(f"request '{e.request_id}' appears twice in one step")
+            seen.add(e.request_id)
+            if len(e.tokens) == 0:
+                raise ValueError(f"request '{e.request_id}': a step entry needs at least one token")
+            for t in e.tokens:
+                if type(t) is not int:
+                    raise ValueError("Token IDs must be integers")
+                if not 0 <= t < self.vocabulary:
+                    raise ValueError(f"token id {t} is outside the model vocabulary "
+                                     f"[0, {self.vocabulary})")
+            for w in e.want:
+                if type(w) is not int or not 0 <= w < len(e.tokens):
+                    raise ValueError(f"request '{e.request_id}': wanted place {w} is not among its "
+                                     f"{len(e.tokens)} tokens")
+
+    def _host_arrays(self, entries: list[StepEntry]) -> SimpleNamespace:
+        lens = np.array([len(e.tokens) for e in entries], dtype=np.int32)
+        n, s = int(lens.sum()), len(entries)
+        pos0 = np.array([self.cache.length(e.request_id) for e in entries], dtype=np.int32)
+        slots = np.array([self.cache.slot(e.request_id) for e in entries], dtype=np.int32)
+        qstart = (np.cumsum(lens) - lens).astype(np.int32)
+        token_seq = np.repeat(np.arange(s, dtype=np.int32), lens)
+        offsets = np.arange(n, dtype=np.int32) - qstart[token_seq]
+        token_ids = np.fromiter((t for e in entries for t in e.tokens), dtype=np.int32, count=n)
+        rows = np.array([qstart[i] + w for i, e in enumerate(entries) for w in e.want],
+                        dtype=np.int32)
+        return SimpleNamespace(
+            n_tokens=n, n_seqs=s, token_ids=token_ids, positions=pos0[token_seq] + offsets,
+            token_slot=slots[token_seq], token_seq=token_seq, seq_slot=slots, seq_qstart=qstart,
+            seq_qlen=lens, seq_pos0=pos0, logit_rows=rows,
+            request_ids=[e.request_id for e in entries])
+
+    _BASE = ("token_ids", "positions", "token_slot", "token_seq", "seq_slot", "seq_qstart",
+             "seq_qlen", "seq_pos0", "logit_rows")
+
+    def _upload(self, host: SimpleNamespace, prep: StepPrep) -> StepContext:
+        arrays = [(name, getattr(host, name)) for name in self._BASE]
+        arrays += list(prep.extra.items())
+        total = sum(_align(a.size) for _, a in arrays)
+        if self._host_meta is None or self._host_meta.numel() < total:
+            cap = max(total * 2, 4096)
+            self._host_meta = torch.empty(cap, dtype=torch.int32).pin_memory()
+            self._dev_meta = torch.empty(cap, dtype=torch.int32, device=self.device)
+        if self._upload_pending:
+            self._uploaded.synchronize()          # the staging buffer is free again
+        stage = self._host_meta.numpy()
+        views: dict[str, torch.Tensor] = {}
+        offset = 0
+        for name, array in arrays:
+            stage[offset: offset + array.size] = array.reshape(-1)
+            views[name] = self._dev_meta[offset: offset + array.size].view(array.shape)
+            offset += _align(array.size)
+        self._dev_meta[:total].copy_(self._host_meta[:total], non_blocking=True)
+        self.cache.flush_tables()
+        self._uploaded.record()
+        self._upload_pending = True
+        return StepContext(
+            device=self.device, dtype=self.dtype, n_tokens=host.n_tokens, n_seqs=host.n_seqs,
+            token_ids=views["token_ids"], positions=views["positions"],
+            token_slot=views["token_slot"], token_seq=views["token_seq"],
+            seq_slot=views["seq_slot"], seq_qstart=views["seq_qstart"],
+            seq_qlen=views["seq_qlen"], seq_pos0=views["seq_pos0"],
+            logit_rows=views["logit_rows"], host=host,
+            arrays={k: v for k, v in views.items() if k not in self._BASE},
+            notes=prep.notes, workspace=self.workspace, status=self.status)
+
+    # ------------------------------------------------------------------ the step
+    def step(self, entries: list[StepEntry]) -> torch.Tensor:
+        """Run the entries as one batch.  Returns logits float32 [wanted, vocabulary] on the
+        device, in the order of the entries and of each entry's ``want``; the tensor is reused by
+        the next step.  Raises ``OutOfPages`` (nothing changed) when the pool cannot hold the
+        step's tokens."""
+        self._validate(entries)
+        admitted = []
+        try:
+            for e in entries:
+                if not self.cache.has(e.request_id):
+                    self.cache.admit(e.request_id)
+                    admitted.append(e.request_id)
+            self.cache.reserve([(e.request_id, self.cache.length(e.request_id) + len(e.tokens))
+                                for e in entries])
+        except Exception:
+            for request_id in admitted:
+                self.cache.release(request_id)
+            raise
+        host = self._host_arrays(entries)
+        prep = StepPrep(host)
+        self.model.prepare(prep)
+        ctx = self._upload(host, prep)
+        logits = self.model.forward(ctx, self.bindings)
+        for e in entries:
+            self.cache.commit(e.request_id, self.cache.length(e.request_id) + len(e.tokens))
+        self.steps_run += 1
+        return logits
+
+    def release(self, request_id: str) -> None:
+        self.cache.release(request_id)
+
+    def check_status(self) -> None:
+        """Synchronises; raises if a kernel skipped work since the last check."""
+        code = int(self.status.item())
+        if code != 0:
+            self.status.zero_()
+            raise KernelStatusError(f"a kernel reported status {code}: a token's position had no "
+                                    f"page in its request's block table")

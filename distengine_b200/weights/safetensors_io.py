@@ -12,6 +12,7 @@ import json
 import mmap
 import os
 import struct
+import warnings
 from typing import Iterator
 
 import numpy as np
@@ -78,7 +79,9 @@ class SafetensorsFile:
                              f"its shape {shape} needs {count * np.dtype(np_dtype).itemsize}")
         array = np.frombuffer(self._map, dtype=np_dtype, count=count,
                               offset=self._data_start + begin)
-        tensor = torch.from_numpy(array.view(np_dtype)) if count else torch.empty(0)
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore", UserWarning)      # the map is read-only, by intent
+            tensor = torch.from_numpy(array) if count else torch.empty(0)
         if torch_dtype == torch.bfloat16:
             tensor = tensor.view(torch.bfloat16)
         return tensor.reshape(shape)

@@ -1,0 +1,113 @@
+"""Helpers of the GPU tests: tolerances, a paged cache built from dense keys and values."""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+# Tolerances, set once.  float32: the engine and the plain implementation differ by the order of
+# float32 additions only.  bfloat16: both round activations to bfloat16 (eps 2^-8) at the same
+# places, but sums are formed in different orders, so roundings flip by one unit here and there and
+# the flips spread through the layers.
+F32_REL = 2e-5          # max |a - b| <= F32_REL * max(1, max |b|)
+BF16_MAX_REL = 4e-2     # max |a - b| <= BF16_MAX_REL * max |b|
+BF16_RMS_REL = 1e-2     # rms(a - b)  <= BF16_RMS_REL * max |b|
+
+
+def assert_close(got, want, dtype: torch.dtype, what: str = "") -> None:
+    got = torch.as_tensor(got, dtype=torch.float32).cpu()
+    want = torch.as_tensor(want, dtype=torch.float32).cpu()
+    assert got.shape == want.shape, f"{what}: shape {tuple(got.shape)} != {tuple(want.shape)}"
+    assert torch.isfinite(got).all(), f"{what}: result is not finite"
+    err = (got - want).abs()
+    scale = want.abs().max().item()
+    if dtype == torch.float32:
+        bound = F32_REL * max(1.0, scale)
+        assert err.max().item() <= bound, (
+            f"{what}: max error {err.max().item():.3e} > {bound:.3e} (scale {scale:.3e}) at "
+            f"{np.unravel_index(int(err.argmax()), tuple(err.shape))}")
+    else:
+        assert err.max().item() <= BF16_MAX_REL * scale, (
+            f"{what}: max error {err.max().item():.3e} > {BF16_MAX_REL * scale:.3e} at "
+            f"{np.unravel_index(int(err.argmax()), tuple(err.shape))}")
+        rms = err.pow(2).mean().sqrt().item()
+        assert rms <= BF16_RMS_REL * scale, f"{what}: rms error {rms:.3e} > {BF16_RMS_REL * scale:.3e}"
+
+
+class PagedFixture:
+    """Dense keys/values of several sequences laid into pages through a scrambled block table.
+    Free pages hold NaN so that a read outside a sequence's own keys shows."""
+
+    def __init__(self, kv_lens, kv_heads, head_dim, page, dtype, device, seed=0, spare_pages=5):
+        g = torch.Generator().manual_seed(seed)
+        self.page, self.kv_lens = page, list(kv_lens)
+        need = [(n + page - 1) // page for n in kv_lens]
+        total = sum(need) + spare_pages
+        order = torch.randperm(total, generator=g).tolist()
+        max_pages = max(need) + 2
+        self.block_table = torch.full((len(kv_lens) + 3, max_pages), -1, dtype=torch.int32)
+        # slots are scrambled too: sequence i lives in slot slots[i]
+        self.slots = torch.randperm(len(kv_lens) + 3, generator=g)[: len(kv_lens)].tolist()
+        self.k = [torch.randn(n, kv_heads, head_dim, generator=g) for n in kv_lens]
+        self.v = [torch.randn(n, kv_heads, head_dim, generator=g) for n in kv_lens]
+        self.k = [t.to(dtype).float() for t in self.k]
+        self.v = [t.to(dtype).float() for t in self.v]
+        self.k_pages = torch.full((total, kv_heads, page, head_dim), float("nan"))
+        self.v_pages = torch.full((total, kv_heads, page, head_dim), float("nan"))
+        at = 0
+        for i, n in enumerate(kv_lens):
+            for p in range(need[i]):
+                pid = order[at]
+                at += 1
+                self.block_table[self.slots[i], p] = pid
+                lo, hi = p * page, min((p + 1) * page, n)
+                self.k_pages[pid, :, : hi - lo] = self.k[i][lo:hi].transpose(0, 1)
+                self.v_pages[pid, :, : hi - lo] = self.v[i][lo:hi].transpose(0, 1)
+        self.dtype, self.device = dtype, device
+
+    def rewrite(self):
+        """Lay self.k / self.v into the pages again (after a test changed them)."""
+        for i, n in enumerate(self.kv_lens):
+            for p in range((n + self.page - 1) // self.page):
+                pid = int(self.block_table[self.slots[i], p])
+                lo, hi = p * self.page, min((p + 1) * self.page, n)
+                self.k_pages[pid, :, : hi - lo] = self.k[i][lo:hi].transpose(0, 1)
+                self.v_pages[pid, :, : hi - lo] = self.v[i][lo:hi].transpose(0, 1)
+
+    def to_device(self):
+        return (self.k_pages.to(self.device, self.dtype).contiguous(),
+                self.v_pages.to(self.device, self.dtype).contiguous(),
+                self.block_table.to(self.device))
+
+
+def run_paged_attention(fx: PagedFixture, q_list, heads, kv_heads, head_dim, scale, window,
+                        chunk=None, chunks_cap=None):
+    """q_list[i]: [q_len_i, heads, d] float32 queries of the LAST q_len_i positions of sequence i.
+    Returns the kernel's output [N, heads*d] float32 (on the CPU)."""
+    from distengine_b200.kernels import attention as ak
+    from distengine_b200.kernels.attention_plan import build_plan
+    dev, dtype = fx.device, fx.dtype
+    qlen = np.array([q.shape[0] for q in q_list], dtype=np.int32)
+    pos0 = np.array([n - ql for n, ql in zip(fx.kv_lens, qlen)], dtype=np.int32)
+    qstart = (np.cumsum(qlen) - qlen).astype(np.int32)
+    rows = ak.rows_per_tile(dtype, head_dim)
+    plan = build_plan(qlen, pos0, heads // kv_heads, kv_heads, rows, window or 0, chunk,
+                      chunks_cap)
+    q = torch.cat([t.reshape(t.shape[0], heads * head_dim) for t in q_list]).to(dev, dtype)
+    # q lives inside a wider row, as in the engine's fused qkv buffer
+    wide = torch.zeros(q.shape[0], heads * head_dim + 2 * kv_heads * head_dim, dtype=dtype,
+                       device=dev)
+    wide[:, : heads * head_dim] = q
+    out = torch.full((q.shape[0], heads * head_dim), float("nan"), dtype=dtype, device=dev)
+    k_pages, v_pages, table = fx.to_device()
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(dev)
+    acc = ml = None
+    if plan.num_partials:
+        n = plan.num_partials * kv_heads * rows
+        acc = torch.full((n * head_dim,), float("nan"), dtype=torch.float32, device=dev)
+        ml = torch.full((n * 2,), float("nan"), dtype=torch.float32, device=dev)
+    ak.paged_attention(wide, out, k_pages, v_pages, table, t(np.array(fx.slots)), t(qstart),
+                       t(qlen), t(pos0), t(plan.items), t(plan.combine), plan.num_partials, rows,
+                       acc, ml, heads, kv_heads, head_dim, scale, window)
+    torch.cuda.synchronize()
+    return out.float().cpu(), plan

@@ -1,0 +1,307 @@
+"""Each kernel alone against its plain reference, at sizes other than the engine's."""
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as plain
+from gpu_helpers import PagedFixture, assert_close, run_paged_attention
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def _ops():
+    from distengine_b200.kernels import ops
+    return ops
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed_rows(dtype):
+    ops = _ops()
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(331, 120, generator=g).to(dtype)
+    ids = torch.randint(0, 331, (37,), generator=g, dtype=torch.int32)
+    out = torch.empty(37, 120, dtype=torch.float32, device=DEV)
+    ops.embed_rows(ids.to(DEV), table.to(DEV), out)
+    assert torch.equal(out.cpu(), plain.plain_embedding(ids, table.float()))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width", [64, 120, 2048, 4100])
+@pytest.mark.parametrize("weight_dtype", DTYPES)
+def test_add_rmsnorm(dtype, width, weight_dtype):
+    ops = _ops()
+    g = torch.Generator().manual_seed(width)
+    n, eps = 19, 3e-6
+    resid = torch.randn(n, width, generator=g) * 3
+    delta = torch.randn(n, width, generator=g).to(dtype)
+    weight = (torch.rand(width, generator=g) + 0.5).to(weight_dtype)
+    want_sum = resid + delta.float()
+    want = plain.plain_rmsnorm(want_sum, weight.float(), eps, dtype)
+
+    r = resid.clone().to(DEV)
+    out = torch.empty(n, width, dtype=dtype, device=DEV)
+    ops.add_rmsnorm(r, delta.to(DEV), weight.to(DEV), eps, out)
+    assert torch.equal(r.cpu(), want_sum)                     # the residual took the sum
+    assert_close(out, want, dtype, "add_rmsnorm")
+
+    # without a branch output
+    out2 = torch.empty(n, width, dtype=dtype, device=DEV)
+    r2 = resid.clone().to(DEV)
+    ops.add_rmsnorm(r2, None, weight.to(DEV), eps, out2)
+    assert torch.equal(r2.cpu(), resid)
+    assert_close(out2, plain.plain_rmsnorm(resid, weight.float(), eps, dtype), dtype, "rmsnorm")
+
+    # picked rows: the residual stays as it was
+    rows = torch.tensor([5, 0, 18, 5], dtype=torch.int32)
+    r3 = resid.clone().to(DEV)
+    out3 = torch.empty(4, width, dtype=dtype, device=DEV)
+    ops.add_rmsnorm(r3, delta.to(DEV), weight.to(DEV), eps, out3, rows.to(DEV))
+    assert torch.equal(r3.cpu(), resid)
+    assert_close(out3, want[rows.long()], dtype, "add_rmsnorm rows")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,d,rot,page", [(4, 2, 16, 16, 16), (3, 3, 32, 32, 8),
+                                                       (6, 1, 48, 48, 32), (5, 5, 80, 32, 4),
+                                                       (8, 2, 128, 128, 64), (2, 1, 256, 256, 16)])
+def test_rope_kv_write(dtype, heads, kv_heads, d, rot, page):
+    ops = _ops()
+    g = torch.Generator().manual_seed(d + page)
+    theta = 25000.0
+    # three sequences; their new tokens start at different positions, one crosses a page's edge
+    starts, lens = [0, page - 1, 3 * page + 2], [5, 4, 1]
+    slots = [2, 0, 3]
+    n = sum(lens)
+    positions = torch.tensor([s + i for s, l in zip(starts, lens) for i in range(l)],
+                             dtype=torch.int32)
+    token_slot = torch.tensor([sl for sl, l in zip(slots, lens) for _ in range(l)],
+                              dtype=torch.int32)
+    num_pages, max_pages = 24, 6
+    table = torch.full((4, max_pages), -1, dtype=torch.int32)
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    for sl in slots:
+        for p in range(max_pages):
+            table[sl, p] = perm.pop()
+    qkv = torch.randn(n, (heads + 2 * kv_heads) * d, generator=g).to(dtype)
+    inv_freq = 1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))
+
+    x = qkv.float().view(n, heads + 2 * kv_heads, d)
+    want_q = x[:, :heads].clone()
+    want_k = x[:, heads: heads + kv_heads].clone()
+    want_q[..., :rot] = plain.plain_rope(want_q[..., :rot], positions, theta, dtype)
+    want_k[..., :rot] = plain.plain_rope(want_k[..., :rot], positions, theta, dtype)
+    want_v = x[:, heads + kv_heads:]
+
+    k_pages = torch.full((num_pages, kv_heads, page, d), float("nan"), dtype=dtype, device=DEV)
+    v_pages = torch.full_like(k_pages, float("nan"))
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    dev_qkv = qkv.to(DEV)
+    ops.rope_kv_write(dev_qkv, positions.to(DEV), token_slot.to(DEV), inv_freq.to(DEV), rot, heads,
+                      kv_heads, d, k_pages, v_pages, table.to(DEV), True, status)
+    assert status.item() == 0
+    got = dev_qkv.float().cpu().view(n, heads + 2 * kv_heads, d)
+    assert_close(got[:, :heads], want_q, dtype, "rotated q")
+    assert torch.equal(got[:, heads:], x[:, heads:]), "k and v in the qkv buffer stay as they were"
+    written = torch.zeros(num_pages, page, dtype=torch.bool)
+    for i in range(n):
+        pos, sl = int(positions[i]), int(token_slot[i])
+        pid = int(table[sl, pos // page])
+        written[pid, pos % page] = True
+        assert_close(k_pages[pid, :, pos % page], want_k[i], dtype, "stored k")
+        assert torch.equal(v_pages[pid, :, pos % page].float().cpu(), want_v[i]), "stored v"
+    # nothing else was touched
+    untouched = ~written[:, None, :, None].expand(-1, kv_heads, -1, d)
+    assert torch.isnan(k_pages.float().cpu()[untouched]).all()
+    assert torch.isnan(v_pages.float().cpu()[untouched]).all()
+
+    # a position without a page is reported, not written
+    bad_table = table.clone()
+    bad_table[slots[0], 0] = -1
+    ops.rope_kv_write(qkv.to(DEV), positions.to(DEV), token_slot.to(DEV), inv_freq.to(DEV), rot,
+                      heads, kv_heads, d, k_pages, v_pages, bad_table.to(DEV), True, status)
+    assert status.item() == 1
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_mul(dtype):
+    ops = _ops()
+    g = torch.Generator().manual_seed(1)
+    x = (torch.randn(23, 2 * 200, generator=g) * 4).to(dtype)
+    out = torch.empty(23, 200, dtype=dtype, device=DEV)
+    ops.silu_mul(x.to(DEV), out)
+    assert_close(out, plain.plain_swiglu(x[:, :200].float(), x[:, 200:].float(), dtype), dtype,
+                 "silu_mul")
+
+
+@pytest.mark.parametrize("n,k,m", [(1, 64, 50), (7, 100, 256), (65, 2051, 331), (130, 176, 64),
+                                   (64, 2048, 2560), (3, 5632, 2048)])
+def test_gemm_f32(n, k, m):
+    ops = _ops()
+    g = torch.Generator().manual_seed(n + k + m)
+    x = torch.randn(n, k, generator=g)
+    w = torch.randn(m, k, generator=g)
+    out = torch.empty(n, m, dtype=torch.float32, device=DEV)
+    ops.gemm_f32(x.to(DEV), w.to(DEV), out)
+    assert_close(out, plain.plain_linear(x, w), torch.float32, "gemm_f32")
+    # a row's result does not depend on the rows beside it
+    one = torch.empty(1, m, dtype=torch.float32, device=DEV)
+    ops.gemm_f32(x[n - 1:].to(DEV), w.to(DEV), one)
+    assert torch.equal(one.cpu()[0], out.cpu()[n - 1])
+
+
+def test_gemm_f32_is_true_32_bit():
+    """Operands with 12 mantissa bits: a 10-bit (TF32) or 8-bit (bfloat16) mantissa would round
+    them to 1 and give exactly k.  Every partial sum n * (1 + 2^-12), n <= 64, fits float32, so
+    the true 32-bit result is exact."""
+    ops = _ops()
+    k = 64
+    x = torch.full((4, k), 1.0 + 2.0 ** -12)
+    w = torch.ones(8, k)
+    out = torch.empty(4, 8, dtype=torch.float32, device=DEV)
+    ops.gemm_f32(x.to(DEV), w.to(DEV), out)
+    assert torch.all(out.cpu() == k * (1.0 + 2.0 ** -12))
+
+
+@pytest.mark.parametrize("n,k,m", [(1, 64, 50), (8, 2048, 2560), (100, 120, 331)])
+def test_linear_bf16(n, k, m):
+    ops = _ops()
+    g = torch.Generator().manual_seed(n)
+    x = torch.randn(n, k, generator=g).to(torch.bfloat16)
+    w = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    got = ops.linear(x.to(DEV), w.to(DEV))
+    assert got.dtype == torch.bfloat16
+    assert_close(got, plain.plain_linear(x.float(), w.float(), torch.bfloat16), torch.bfloat16,
+                 "linear bf16")
+    wide = ops.linear(x.to(DEV), w.to(DEV), out_dtype=torch.float32)
+    assert wide.dtype == torch.float32
+    assert_close(wide, plain.plain_linear(x.float(), w.float(), torch.bfloat16, keep_f32=True),
+                 torch.float32, "linear bf16 -> f32")
+
+
+def test_sample_rows_greedy_and_ties():
+    ops = _ops()
+    g = torch.Generator().manual_seed(0)
+    logits = torch.randn(9, 32003, generator=g)
+    logits[3, 100] = logits[3, 31000] = 50.0             # a tie: the lowest id wins
+    logits[4, 32002] = 60.0                              # the last id
+    logits[5, 0] = 60.0
+    out = torch.empty(9, dtype=torch.int32, device=DEV)
+    ops.sample_rows(logits.to(DEV), out)
+    want = [plain.plain_greedy(row) for row in logits]
+    assert out.cpu().tolist() == want
+    assert want[3] == 100 and want[4] == 32002 and want[5] == 0
+
+
+def test_sample_rows_temperature_matches_plain_and_softmax():
+    ops = _ops()
+    g = torch.Generator().manual_seed(5)
+    vocab = 331
+    logits = torch.randn(6, vocab, generator=g) * 2
+    temperature = torch.tensor([0.8, 0.0, 1.5, 0.8, 0.3, 1.0])
+    seed = torch.tensor([7, 7, 123456789012, 8, 7, -3], dtype=torch.int64)
+    position = torch.tensor([5, 5, 70, 5, 6, 0], dtype=torch.int32)
+    out = torch.empty(6, dtype=torch.int32, device=DEV)
+    ops.sample_rows(logits.to(DEV), out, temperature.to(DEV), seed.to(DEV), position.to(DEV))
+    want = [plain.plain_temperature_sample(logits[r], float(temperature[r]), int(seed[r]),
+                                           int(position[r])) for r in range(6)]
+    assert out.cpu().tolist() == want
+    # the draws follow softmax(logits / T): 4000 positions of one row
+    rows = 4000
+    many = logits[0:1].expand(rows, vocab).contiguous()
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    ops.sample_rows(many.to(DEV), out, torch.full((rows,), 0.8, device=DEV),
+                    torch.full((rows,), 11, dtype=torch.int64, device=DEV),
+                    torch.arange(rows, dtype=torch.int32, device=DEV))
+    counts = torch.bincount(out.cpu().long(), minlength=vocab).float()
+    probs = plain.softmax_probabilities(logits[0], 0.8)
+    top = torch.topk(probs, 5).indices
+    for i in top.tolist():
+        expect = probs[i].item() * rows
+        assert abs(counts[i].item() - expect) <= 5 * np.sqrt(expect) + 3, (i, counts[i], expect)
+
+
+# ----------------------------------------------------------------------------- attention
+def _plain_attention_case(fx, q_list, heads, kv_heads, d, scale, window, dtype):
+    outs = []
+    for i, q in enumerate(q_list):
+        n, ql = fx.kv_lens[i], q.shape[0]
+        qpos = torch.arange(n - ql, n)
+        outs.append(plain.plain_attention(q, fx.k[i], fx.v[i], qpos, window, dtype, scale)
+                    .reshape(ql, heads * d))
+    return torch.cat(outs)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,d,page", [(4, 2, 16, 16), (3, 3, 32, 8), (6, 1, 48, 32),
+                                                   (8, 1, 64, 16), (5, 5, 80, 4), (16, 2, 128, 64),
+                                                   (2, 1, 256, 16), (32, 4, 64, 16)])
+def test_paged_attention_mixed_batch(dtype, heads, kv_heads, d, page):
+    """Prompt portions beside decoded tokens, scrambled block tables, NaN in every free page."""
+    g = torch.Generator().manual_seed(heads * d + page)
+    kv_lens = [130, 1, 77, 300, 33]
+    q_lens = [130, 1, 1, 21, 2]             # whole prompt, first token, decode, portion, two tokens
+    fx = PagedFixture(kv_lens, kv_heads, d, page, dtype, DEV, seed=d)
+    q_list = [torch.randn(ql, heads, d, generator=g).to(dtype).float() for ql in q_lens]
+    scale = d ** -0.5
+    want = _plain_attention_case(fx, q_list, heads, kv_heads, d, scale, None, dtype)
+    got, plan = run_paged_attention(fx, q_list, heads, kv_heads, d, scale, None, chunk=0)
+    assert plan.num_partials == 0
+    assert_close(got, want, dtype, "paged attention")
+    got, plan = run_paged_attention(fx, q_list, heads, kv_heads, d, scale, None)
+    assert_close(got, want, dtype, "paged attention, chunk chosen by the plan")
+    # the same with every key range cut into chunks of 64 and merged
+    got, plan = run_paged_attention(fx, q_list, heads, kv_heads, d, scale, None, chunk=64)
+    assert plan.num_partials > 0
+    assert_close(got, want, dtype, "paged attention, split keys")
+    # and with the fixed-shape plan that a replayed graph uses
+    got, plan = run_paged_attention(fx, q_list, heads, kv_heads, d, scale, None, chunk=128,
+                                    chunks_cap=4)
+    assert_close(got, want, dtype, "paged attention, capped chunks")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("d,page,window", [(32, 8, 24), (64, 16, 100), (48, 16, 16)])
+def test_paged_attention_window(dtype, d, page, window):
+    heads, kv_heads = 4, 2
+    g = torch.Generator().manual_seed(window)
+    kv_lens, q_lens = [200, 90, 17], [1, 40, 17]
+    fx = PagedFixture(kv_lens, kv_heads, d, page, dtype, DEV, seed=window)
+    q_list = [torch.randn(ql, heads, d, generator=g).to(dtype).float() for ql in q_lens]
+    # the key just outside the first sequence's window would dominate if it were read, and the
+    # first key inside must be read
+    edge = kv_lens[0] - window
+    fx.k[0][edge - 1] = q_list[0][0, :kv_heads] * 4
+    fx.k[0][edge] = q_list[0][0, :kv_heads] * 2
+    fx.rewrite()
+    want = _plain_attention_case(fx, q_list, heads, kv_heads, d, d ** -0.5, window, dtype)
+    for chunk in (0, None, 64):
+        got, _ = run_paged_attention(fx, q_list, heads, kv_heads, d, d ** -0.5, window, chunk=chunk)
+        assert_close(got, want, dtype, f"windowed attention chunk={chunk}")
+    # pages wholly behind the window may be gone from the table: same result
+    first_kept = (kv_lens[0] - window + 1) // page
+    for p in range(first_kept):
+        fx.block_table[fx.slots[0], p] = -1
+    got, _ = run_paged_attention(fx, q_list, heads, kv_heads, d, d ** -0.5, window, chunk=0)
+    assert_close(got, want, dtype, "windowed attention, released pages")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("far", [0, 15, 16, 511, 512, 1023, 1100])
+def test_paged_attention_one_far_key_stands_out(dtype, far):
+    """One key among 1101 is made to dominate one head's softmax: the output must be that key's
+    value.  A wrong page, offset or tile edge would show as a different value."""
+    heads, kv_heads, d, page = 8, 2, 64, 16
+    g = torch.Generator().manual_seed(far)
+    fx = PagedFixture([1101], kv_heads, d, page, dtype, DEV, seed=far)
+    q = torch.randn(1, heads, d, generator=g).to(dtype).float()
+    q[0, 5] = q[0, 5] / q[0, 5].norm() * 8
+    fx.k[0][far, 1] = (q[0, 5] * 4).to(dtype).float()         # head 5 reads kv head 1
+    fx.rewrite()
+    want = _plain_attention_case(fx, [q], heads, kv_heads, d, d ** -0.5, None, dtype)
+    assert torch.allclose(want[0, 5 * d: 6 * d], fx.v[0][far, 1], atol=2e-2)
+    for chunk in (0, 256):
+        got, _ = run_paged_attention(fx, [q], heads, kv_heads, d, d ** -0.5, None, chunk=chunk)
+        assert_close(got, want, dtype, f"far key {far} chunk={chunk}")
