@@ -1,0 +1,297 @@
+"""Decode and prefill throughput of the engine on one B200, TinyLlama-1.1B layer sizes, random
+weights, bfloat16.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one decode step of a batch of 8 requests whose prompts of 512 tokens are in the cache;
+K steps are timed with CUDA events after W warm-up steps.  One JSON line is printed:
+
+* ``value``: decoded tokens a second of the step function fed from the host with fixed tokens (no
+  read-back between steps);
+* ``e2e``: the same through the Python entry point (``Engine.submit`` / ``Engine.step``): every
+  step uploads its arrays from pinned host memory and reads the sampled tokens back;
+* ``prefill``: one prompt of 2,048 tokens in one step;
+* ``roofline``: bytes a decode step has to read (every weight once, the live requests' cache)
+  over its time, against the measured copy bandwidth;
+* ``points``: decode at batch 1 and 64.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# BASELINE.json configs[2]: TinyLlama-1.1B shape
+MODEL = dict(architectures=["LlamaForCausalLM"], vocab_size=32000, hidden_size=2048,
+             intermediate_size=5632, num_hidden_layers=22, num_attention_heads=32,
+             num_key_value_heads=4, rms_norm_eps=1e-5, rope_theta=10000.0,
+             max_position_embeddings=2048, tie_word_embeddings=False)
+PROMPT, NEW_TOKENS, PREFILL, PAGE = 512, 128, 2048, 16
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks() -> tuple[dict, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as handle:
+                data = json.load(handle)
+            flat = {}
+
+            def walk(node):
+                if isinstance(node, dict):
+                    for k, v in node.items():
+                        if isinstance(v, (int, float)) and not isinstance(v, bool):
+                            flat.setdefault(k, float(v))
+                        else:
+                            walk(v)
+            walk(data)
+            if "hbm_gbs" in flat and "bf16_tflops" in flat:
+                return flat, "measured"
+        except (OSError, ValueError):
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+
+    def __init__(self) -> None:
+        self.lines: list[str] = []
+        self.proc = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self) -> dict:
+        sm, top, reasons = [], [], set()
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(int(parts[0]))
+                top.append(int(parts[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(self.NAMES, parts[2:6]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": int(statistics.median(sm)), "sm_max_mhz": max(top),
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def model_folder() -> str:
+    """The random-weights model folder (written once per machine into the temporary folder)."""
+    from distengine_b200.weights import write_random_model
+    folder = os.path.join(tempfile.gettempdir(), f"distengine_b200-bench-{os.getuid()}",
+                          "tinyllama-shape-seed0-bf16")
+    marker = os.path.join(folder, ".complete")
+    if not os.path.isfile(marker):
+        print("[bench] writing the random-weights model folder ...", file=sys.stderr, flush=True)
+        write_random_model(MODEL, folder, seed=0, dtype="bfloat16")
+        with open(marker, "w") as handle:
+            handle.write("ok")
+    return folder
+
+
+def weight_bytes(model) -> tuple[int, int]:
+    """(bytes of all weights a decode step reads once, matrix parameters in the layers)."""
+    total = model.output.numel() * model.output.element_size()
+    params = 0
+    for block in model.blocks:
+        mixer, ffn = block.mixer, block.feed_forward
+        for t in (mixer.w_qkv, mixer.w_o, ffn.w_gate_up, ffn.w_down):
+            total += t.numel() * t.element_size()
+            params += t.numel()
+        for norm in (block.mixer_norm, block.feed_forward_norm):
+            total += norm.weight.numel() * norm.weight.element_size()
+    return total, params
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=NEW_TOKENS)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--batch", type=int, default=8)
+    args = parser.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference does not install offline: its build backend "
+                          "'hatchling' is neither installed nor in the wheelhouse"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not measured")
+        return 2
+    warmup, steps = max(args.warmup, 3), max(args.steps, 1)
+
+    import numpy as np
+    import torch
+
+    from distengine_b200 import Engine, EngineConfig
+    from distengine_b200.engine.step import StepEntry
+    from distengine_b200.kernels import ops
+
+    peak, peak_kind = peaks()
+    folder = model_folder()
+    rng = np.random.default_rng(0)
+    vocab = MODEL["vocab_size"]
+    pages = (64 * (PROMPT + 3 + 2 * NEW_TOKENS + steps) + PREFILL) // PAGE + 64
+    engine = Engine(folder, EngineConfig(dtype="bfloat16", block_size=PAGE, num_blocks=pages,
+                                         decode_batch_size=64, max_batch_tokens=PREFILL))
+    runner, model = engine.runner, engine.model
+    w_bytes, layer_params = weight_bytes(model)
+    kv_per_token = sum(2 * g.k.shape[0] * g.spec.kv_heads * g.spec.head_dim * g.k.element_size()
+                       for g in engine.cache.paged)
+
+    def tokens(n):
+        return [int(t) for t in rng.integers(0, vocab, size=n)]
+
+    # ------------------------------------------------------------------ prefill of 2,048 tokens
+    def prefill_once():
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        entry = StepEntry("prefill", tokens(PREFILL), [PREFILL - 1])
+        torch.cuda.synchronize()
+        start.record()
+        runner.step([entry])
+        stop.record()
+        torch.cuda.synchronize()
+        runner.release("prefill")
+        return start.elapsed_time(stop)
+
+    for _ in range(3):
+        prefill_once()
+    prefill_ms = statistics.median(prefill_once() for _ in range(5))
+    cfg = model.config
+    attn_flops = (4 * cfg.head_dim * cfg.num_attention_heads * PREFILL * (PREFILL + 1) // 2
+                  * cfg.num_hidden_layers)
+    prefill_flops = 2 * PREFILL * layer_params + attn_flops + 2 * vocab * cfg.hidden_size
+    prefill = {"value": round(PREFILL / prefill_ms * 1e3, 1), "tokens": PREFILL,
+               "ms": round(prefill_ms, 3),
+               "frac": round(prefill_flops / (prefill_ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4)}
+
+    # ------------------------------------------------------------------ decode, device-timed
+    def decode(batch, k_steps, w_steps, sample_clocks=False):
+        ids = [f"d{batch}-{i}" for i in range(batch)]
+        for rid in ids:                                   # prompts into the cache
+            runner.step([StepEntry(rid, tokens(PROMPT), [])])
+        feed = [[StepEntry(rid, [int(t)], [0]) for rid, t in zip(ids, row)]
+                for row in rng.integers(0, vocab, size=(w_steps + k_steps, batch))]
+        for entries in feed[:w_steps]:
+            ops.sample_rows(runner.step(entries), engine.sampler.ids[:batch])
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        launches = ops.launch_count
+        sampler = ClockSampler() if sample_clocks else None
+        if sampler:
+            sampler.__enter__()
+        start.record()
+        for entries in feed[w_steps:]:
+            ops.sample_rows(runner.step(entries), engine.sampler.ids[:batch])
+        stop.record()
+        torch.cuda.synchronize()
+        if sampler:
+            sampler.__exit__()
+        ms = start.elapsed_time(stop) / k_steps
+        launches = ops.launch_count - launches
+        context = PROMPT + w_steps + (k_steps - 1) / 2 + 1          # mean keys read per request
+        for rid in ids:
+            runner.release(rid)
+        runner.check_status()
+        return ms, launches, context, (sampler.summary() if sampler else None)
+
+    ms, launches, context, clocks = decode(args.batch, steps, warmup, sample_clocks=True)
+    step_bytes = w_bytes + args.batch * context * kv_per_token + args.batch * cfg.hidden_size * 2
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    points = {}
+    for b in (1, 64):
+        b_ms, _, _, _ = decode(b, min(steps, NEW_TOKENS), warmup)
+        points[f"decode_b{b}"] = round(b / b_ms * 1e3, 1)
+
+    # ------------------------------------------------------------------ end to end
+    for i in range(args.batch):
+        engine.submit(f"e2e-{i}", tokens(PROMPT), warmup + steps + 1, -1)
+    while any(r.num_computed < PROMPT for r in engine.requests.values()) or engine.steps == 0:
+        engine.step()
+    for _ in range(warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        engine.step()
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    h2d = runner.upload_bytes
+    while engine.has_pending():
+        engine.step()
+
+    record = {
+        "metric": "decode tokens/s at batch 8 (TinyLlama-1.1B shape, 512-token prompts, 1 B200)",
+        "value": round(args.batch / ms * 1e3, 1), "unit": "tokens/s", "n_gpus": 1,
+        "steps": steps, "warmup": warmup, "ms_per_step": round(ms, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "impl": "ours",
+        "config": {"model": "TinyLlama-1.1B shape, random weights N(0,0.02) seed 0",
+                   "layers": cfg.num_hidden_layers, "layers_of_config": 22,
+                   "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads,
+                   "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
+                   "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+                   "global_batch": args.batch, "seq_len": PROMPT, "new_tokens": steps,
+                   "max_position": cfg.max_position_embeddings, "page_size": PAGE,
+                   "parallelism": "single GPU", "cuda_graphs": bool(runner.graph_replays),
+                   "l2": "inputs larger than L2: 2.07 GB of weights are read every step",
+                   "peaks": peak_kind},
+        "clocks": clocks,
+        "e2e": {"value": round(args.batch * steps / e2e_s, 1), "unit": "tokens/s",
+                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": 4 * args.batch},
+        "gpu_launches": int(launches),
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"],
+                     "unit": "GB/s", "frac": round(achieved / peak["hbm_gbs"], 4)},
+        "points": points,
+    }
+    print(json.dumps(record))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

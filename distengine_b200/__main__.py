@@ -1,0 +1,127 @@
+"""Command line: ``python -m distengine_b200 <command>``.
+
+``generate`` follows the reference's ``utils.manual_generate`` (src/utils/manual_generate.py:10-58):
+``--prompt`` and ``--max-new-tokens`` (default 32, must be positive) keep their names and
+meanings, and it prints the generated token ids and, with a tokenizer, the decoded text.  The
+reference downloads its model and tokenizer; here ``--model`` names a folder, ``--prompt-ids``
+gives token ids directly, and ``--prompt`` needs a ``tokenizer.json`` in the model folder.
+``--decode-batch-size`` is the reference's benchmark flag (src/utils/benchmark.py:593).
+``random-model`` writes a model folder from a configuration and a seed.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+
+def _tokenizer(model_dir: str):
+    path = os.path.join(model_dir, "tokenizer.json")
+    if not os.path.isfile(path):
+        return None
+    try:
+        from tokenizers import Tokenizer
+    except ImportError:
+        return None
+    return Tokenizer.from_file(path)
+
+
+def _generate(args: argparse.Namespace) -> int:
+    if args.max_new_tokens <= 0:
+        raise SystemExit("--max-new-tokens must be positive")
+    from .config.engine import EngineConfig
+    from .engine.engine import Engine
+
+    tokenizer = _tokenizer(args.model)
+    prompts: list[list[int]] = []
+    for text in args.prompt_ids or []:
+        prompts.append([int(t) for t in text.replace(",", " ").split()])
+    for text in args.prompt or []:
+        if tokenizer is None:
+            raise SystemExit(f"--prompt needs {os.path.join(args.model, 'tokenizer.json')} and "
+                             f"the 'tokenizers' package; give token ids with --prompt-ids instead")
+        prompts.append(tokenizer.encode(text).ids)
+    if not prompts:
+        raise SystemExit("give at least one --prompt-ids or --prompt")
+
+    config = EngineConfig(dtype=args.dtype, block_size=args.block_size,
+                          num_blocks=args.num_blocks, decode_batch_size=args.decode_batch_size,
+                          max_batch_tokens=args.max_batch_tokens, device=args.device)
+    engine = Engine(args.model, config)
+    eos = args.eos_token_id
+    if eos is None:
+        eos = engine.model.config.eos_token_id if getattr(engine.model.config, "eos_token_id",
+                                                          None) is not None else -1
+    outputs = engine.generate(prompts, args.max_new_tokens, eos, args.temperature, args.seed)
+    for generated in outputs:
+        print("Generated token IDs:", generated)
+        if tokenizer is not None:
+            print(tokenizer.decode(generated, skip_special_tokens=True))
+    return 0
+
+
+def _random_model(args: argparse.Namespace) -> int:
+    from .weights.random_init import write_random_model
+    with open(args.config) as handle:
+        config = json.load(handle)
+    write_random_model(config, args.out, args.seed, dtype=args.dtype, norm_init=args.norm_init)
+    print(f"wrote {args.out}/config.json and {args.out}/model.safetensors")
+    return 0
+
+
+def _replay(args: argparse.Namespace) -> int:
+    from .engine.replay import build_runner, replay
+    runner = build_runner(args.model, args.dtype, args.max_tokens, args.block_size, args.device)
+    replay(runner, sys.stdin, args.out)
+    return 0
+
+
+def main(argv: "list[str] | None" = None) -> int:
+    parser = argparse.ArgumentParser(prog="distengine_b200", description=__doc__,
+                                     formatter_class=argparse.RawDescriptionHelpFormatter)
+    sub = parser.add_subparsers(dest="command", required=True)
+
+    gen = sub.add_parser("generate", help="generate tokens for one or more prompts")
+    gen.add_argument("--model", required=True, help="folder with config.json, model.safetensors")
+    gen.add_argument("--prompt", action="append", help="prompt text (needs tokenizer.json)")
+    gen.add_argument("--prompt-ids", action="append",
+                     help="prompt as token ids, separated by spaces or commas; may repeat")
+    gen.add_argument("--max-new-tokens", type=int, default=32)
+    gen.add_argument("--temperature", type=float, default=0.0, help="0: greedy")
+    gen.add_argument("--seed", type=int, default=0, help="sampling seed of the first prompt")
+    gen.add_argument("--eos-token-id", type=int, default=None,
+                     help="default: the configuration's, else none (-1)")
+    gen.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    gen.add_argument("--block-size", type=int, default=16, help="tokens in a page of the cache")
+    gen.add_argument("--num-blocks", type=int, default=None, help="pages in the pool")
+    gen.add_argument("--decode-batch-size", type=int, default=64,
+                     help="most requests live at a time")
+    gen.add_argument("--max-batch-tokens", type=int, default=2048, help="token budget of a step")
+    gen.add_argument("--device", default="cuda:0")
+    gen.set_defaults(run=_generate)
+
+    rnd = sub.add_parser("random-model", help="write a model folder with random weights")
+    rnd.add_argument("--config", required=True, help="a config.json to take the sizes from")
+    rnd.add_argument("--out", required=True)
+    rnd.add_argument("--seed", type=int, default=0)
+    rnd.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    rnd.add_argument("--norm-init", default="ones", choices=["ones", "uniform"])
+    rnd.set_defaults(run=_random_model)
+
+    rep = sub.add_parser("replay", help="trace replay (same as bin/trace_run)")
+    rep.add_argument("--model", required=True)
+    rep.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
+    rep.add_argument("--out", required=True)
+    rep.add_argument("--max-tokens", type=int, required=True)
+    rep.add_argument("--block-size", type=int, default=16)
+    rep.add_argument("--device", default="cuda:0")
+    rep.set_defaults(run=_replay)
+
+    args = parser.parse_args(argv)
+    return args.run(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -57,6 +57,11 @@ class StepRunner:
         self.bindings = cache.bindings()
         self.use_graphs = use_graphs
         self.steps_run = 0
+        self.last_arrays: dict[str, torch.Tensor] = {}
+        # decode steps replayed as CUDA graphs: key -> (graph, logits, kernels in it, generation)
+        self._graphs: dict[tuple, tuple] = {}
+        self._meta_generation = 0
+        self.graph_replays = 0
 
     # ------------------------------------------------------------------ host side
     def _validate(self, entries: list[StepEntry]) -> None:
@@ -110,6 +115,8 @@ class StepRunner:
             cap = max(total * 2, 4096)
             self._host_meta = torch.empty(cap, dtype=torch.int32).pin_memory()
             self._dev_meta = torch.empty(cap, dtype=torch.int32, device=self.device)
+            self._meta_generation += 1
+        self.upload_bytes = total * 4
         if self._upload_pending:
             self._uploaded.synchronize()          # the staging buffer is free again
         stage = self._host_meta.numpy()
@@ -134,9 +141,11 @@ class StepRunner:
             notes=prep.notes, workspace=self.workspace, status=self.status)
 
     # ------------------------------------------------------------------ the step
-    def step(self, entries: list[StepEntry]) -> torch.Tensor:
-        """Run the entries as one batch.  Returns logits float32 [wanted, vocabulary] on the
-        device, in the order of the entries and of each entry's ``want``; the tensor is reused by
+    def step(self, entries: list[StepEntry],
+             extra: "dict[str, np.ndarray] | None" = None) -> torch.Tensor:
+        """Run the entries as one batch.  ``extra``: int32 arrays of the caller's that travel to
+        the device with the step's own arrays (``self.last_arrays[name]`` afterwards).
+        Returns logits float32 [wanted, vocabulary] on the device, in the order of the entries and of each entry's ``want``; the tensor is reused by
         the next step.  Raises ``OutOfPages`` (nothing changed) when the pool cannot hold the
         step's tokens."""
         self._validate(entries)
@@ -153,13 +162,58 @@ class StepRunner:
                 self.cache.release(request_id)
             raise
         host = self._host_arrays(entries)
-        prep = StepPrep(host)
+        graph_shape = None
+        if (self.use_graphs and int(host.seq_qlen.max()) == 1
+                and getattr(self.model, "graph_safe", True)):
+            # a pure decode step: shape its arrays by the batch's shape only, so that it can be
+            # replayed; the key range is capped at the next multiple of 512 positions
+            longest = int(host.seq_pos0.max()) + 1
+            graph_shape = {"context_cap": (longest + 511) // 512 * 512}
+        prep = StepPrep(host, graph_shape)
         self.model.prepare(prep)
+        for name, array in (extra or {}).items():
+            prep.add(name, array)
         ctx = self._upload(host, prep)
-        logits = self.model.forward(ctx, self.bindings)
+        self.last_arrays = ctx.arrays
+        if graph_shape is None:
+            logits = self.model.forward(ctx, self.bindings)
+        else:
+            logits = self._forward_graphed(ctx, prep, graph_shape)
         for e in entries:
             self.cache.commit(e.request_id, self.cache.length(e.request_id) + len(e.tokens))
         self.steps_run += 1
+        return logits
+
+    def _forward_graphed(self, ctx: StepContext, prep: StepPrep, graph_shape: dict) -> torch.Tensor:
+        """Replay the decode step of this shape as a CUDA graph; the first step of a shape runs
+        as it is (which also brings every scratch buffer to its size), the second is captured.
+        The graph reads the step's arrays from the same device addresses every time; only their
+        contents change."""
+        key = (ctx.n_seqs, graph_shape["context_cap"], ctx.logit_rows.shape[0],
+               tuple((name, array.shape) for name, array in prep.extra.items()),
+               tuple(sorted(prep.notes.items())))
+        stamp = (self.workspace.generation, self._meta_generation)
+        entry = self._graphs.get(key)
+        if entry is not None and entry[3] != stamp:
+            self._graphs.clear()                       # buffers moved: every graph is stale
+            entry = None
+        if entry is None:
+            logits = self.model.forward(ctx, self.bindings)
+            self._graphs[key] = (None, logits, 0, (self.workspace.generation,
+                                                    self._meta_generation))
+            return logits
+        graph, logits, kernels, _ = entry
+        if graph is None:
+            graph = torch.cuda.CUDAGraph()
+            before = ops.launch_count
+            with torch.cuda.graph(graph):
+                logits = self.model.forward(ctx, self.bindings)
+            kernels = ops.launch_count - before
+            ops.launch_count = before
+            self._graphs[key] = (graph, logits, kernels, stamp)
+        graph.replay()
+        ops.launch_count += kernels
+        self.graph_replays += 1
         return logits
 
     def release(self, request_id: str) -> None:

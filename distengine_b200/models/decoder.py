@@ -98,6 +98,10 @@ class DecoderModel:
         return out
 
     # ------------------------------------------------------------------ step
+    @property
+    def graph_safe(self) -> bool:
+        return all(part.graph_safe for block in self.blocks for part in block.parts().values())
+
     def prepare(self, prep: StepPrep) -> None:
         for block in self.blocks:
             for part in block.parts().values():

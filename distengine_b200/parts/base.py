@@ -42,6 +42,10 @@ class StateSpec:
 class Part:
     """Base of all parts."""
 
+    # False for a part whose forward depends on the step's host arrays (Python control flow over
+    # sequences): its steps are then never captured into a CUDA graph
+    graph_safe = True
+
     def __init__(self, dtype: torch.dtype, device: torch.device) -> None:
         self.dtype = dtype
         self.device = device

@@ -29,6 +29,7 @@ class Workspace:
     def __init__(self, device: torch.device) -> None:
         self.device = device
         self._buffers: dict[str, torch.Tensor] = {}
+        self.generation = 0          # grows whenever a buffer moves: captured graphs are stale then
 
     def get(self, name: str, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
         count = 1
@@ -39,6 +40,7 @@ class Workspace:
             grow = count if buf is None or buf.dtype != dtype else max(count, 2 * buf.numel())
             buf = torch.empty(max(grow, 1), dtype=dtype, device=self.device)
             self._buffers[name] = buf
+            self.generation += 1
         return buf[:count].view(shape)
 
     def bytes(self) -> int:

@@ -1,0 +1,53 @@
+"""Sampling the next token of each finished portion: greedy and temperature.
+
+Greedy is the reference's only sampler: arg-max over the vocabulary
+(src/layers/sampler.py:5-8); the lowest id wins a tie.  Temperature sampling draws from
+softmax(logits / T), computed in 32-bit, by the Gumbel-max rule with counter-based uniforms of
+(seed, position of the sampled token, token id): a request's draws depend on its own seed and
+position only, not on the batch it shares or on how its prompt was cut.  Temperature 0 is greedy.
+Both run in one kernel over the step's logits rows; the sampled ids come back in one small copy.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from ..kernels import ops
+
+
+def pack_sampling(temperatures: list[float], seeds: list[int], positions: list[int]):
+    """int32 arrays that carry float32 temperatures, int64 seeds and int32 positions to the
+    device inside the step's upload, or None when every row is greedy."""
+    if not any(t > 0.0 for t in temperatures):
+        return None
+    t = np.asarray(temperatures, dtype=np.float32).view(np.int32)
+    s = np.asarray([np.int64(x) for x in seeds], dtype=np.int64).view(np.int32)
+    p = np.asarray(positions, dtype=np.int32)
+    return {"sampling/temperature": t, "sampling/seed": s, "sampling/position": p}
+
+
+class Sampler:
+    def __init__(self, device: torch.device, max_rows: int) -> None:
+        self.device = device
+        self.ids = torch.zeros(max_rows, dtype=torch.int32, device=device)
+        self.host_ids = torch.zeros(max_rows, dtype=torch.int32).pin_memory()
+
+    def sample(self, logits: torch.Tensor, arrays: "dict[str, torch.Tensor] | None") -> list[int]:
+        """Token ids for the rows of ``logits`` [R, V]; synchronises to bring them to the host."""
+        rows = logits.shape[0]
+        if rows == 0:
+            return []
+        if rows > self.ids.shape[0]:
+            self.ids = torch.zeros(2 * rows, dtype=torch.int32, device=self.device)
+            self.host_ids = torch.zeros(2 * rows, dtype=torch.int32).pin_memory()
+        out = self.ids[:rows]
+        if arrays and "sampling/temperature" in arrays:
+            ops.sample_rows(logits, out, arrays["sampling/temperature"].view(torch.float32),
+                            arrays["sampling/seed"].view(torch.int64),
+                            arrays["sampling/position"])
+        else:
+            ops.sample_rows(logits, out)
+        self.host_ids[:rows].copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self.host_ids[:rows].tolist()

@@ -111,3 +111,43 @@ def run_paged_attention(fx: PagedFixture, q_list, heads, kv_heads, head_dim, sca
                        acc, ml, heads, kv_heads, head_dim, scale, window)
     torch.cuda.synchronize()
     return out.float().cpu(), plan
+
+
+class PartHarness:
+    """Runs single parts through the engine's own step machinery (``StepRunner`` and
+    ``CacheManager``): ``run(entries, fn)`` calls ``fn(ctx, bindings)`` with the step's context."""
+
+    class _Config:
+        def __init__(self, vocabulary, width):
+            self.vocabulary, self.width = vocabulary, width
+
+    class _Model:
+        def __init__(self, parts, dtype, device, vocabulary, width):
+            self.parts, self.dtype, self.device = parts, dtype, torch.device(device)
+            self.config = PartHarness._Config(vocabulary, width)
+            self.fn = None
+
+        def prepare(self, prep):
+            for part in self.parts:
+                part.prepare(prep)
+
+        def forward(self, ctx, bindings):
+            return self.fn(ctx, bindings)
+
+    def __init__(self, parts, cache_specs, dtype, page_size=16, num_pages=64, max_seqs=8,
+                 max_len=1024, device="cuda:0", reads=None, vocabulary=1000, width=1):
+        from distengine_b200.cache import CacheManager
+        from distengine_b200.engine.step import StepRunner
+        self.model = self._Model(parts, dtype, device, vocabulary, width)
+        self.cache = CacheManager(cache_specs, reads or [None] * len(cache_specs), page_size,
+                                  num_pages, max_seqs, max_len, dtype, device,
+                                  poison_freed_pages=True)
+        self.runner = StepRunner(self.model, self.cache)
+
+    def run(self, entries, fn):
+        """entries: list of (request id, number of new tokens)."""
+        from distengine_b200.engine.step import StepEntry
+        self.model.fn = fn
+        out = self.runner.step([StepEntry(rid, [0] * n, []) for rid, n in entries])
+        self.runner.check_status()
+        return out

@@ -1,0 +1,69 @@
+"""The plain implementation against the committed outputs of the reference's own model code
+(tests/golden/make_golden.py made them), and its own consistency."""
+
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as plain
+import tiny_configs
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+def test_plain_matches_reference_outputs(name, model_root):
+    folder = tiny_configs.make_folder(name, model_root)
+    config, weights = plain.load_model_folder(folder)
+    golden = np.load(os.path.join(GOLDEN, f"{name}.npz"))
+    ids = [int(t) for t in golden["token_ids"]]
+    assert ids == tiny_configs.prompt_tokens(name, len(ids))
+    logits = plain.plain_forward(config, weights, ids).numpy()
+    scale = np.abs(golden["logits"]).max()
+    assert np.abs(logits - golden["logits"]).max() <= 2e-6 * max(1.0, scale)
+
+
+def test_prefix_logits_do_not_depend_on_what_follows(model_root):
+    folder = tiny_configs.make_folder("tiny_c", model_root)
+    config, weights = plain.load_model_folder(folder)
+    ids = tiny_configs.prompt_tokens("tiny_c", 40)
+    whole = plain.plain_forward(config, weights, ids)
+    part = plain.plain_forward(config, weights, ids[:23])
+    assert torch.allclose(whole[:23], part, atol=1e-6)
+
+
+def test_rope_is_half_split_rotation():
+    x = torch.zeros(1, 1, 8)
+    x[0, 0, 1] = 1.0                      # feature 1 pairs with feature 5
+    out = plain.plain_rope(x, torch.tensor([3]), 10000.0)
+    angle = 3.0 * plain.plain_inv_freq(8, 10000.0)[1]
+    assert torch.allclose(out[0, 0, 1], torch.cos(angle)) and torch.allclose(out[0, 0, 5],
+                                                                            torch.sin(angle))
+    assert out[0, 0, [0, 2, 3, 4, 6, 7]].abs().max() == 0
+
+
+def test_attention_mask_and_window():
+    g = torch.Generator().manual_seed(0)
+    q, k, v = (torch.randn(6, 2, 4, generator=g) for _ in range(3))
+    pos = torch.arange(6)
+    full = plain.plain_attention(q, k, v, pos)
+    # the first query sees only the first key
+    assert torch.allclose(full[0], v[0])
+    # a window of 1 sees only the query's own key
+    assert torch.allclose(plain.plain_attention(q, k, v, pos, window=1), v)
+    # a window that covers everything changes nothing
+    assert torch.allclose(plain.plain_attention(q, k, v, pos, window=6), full)
+
+
+def test_sampling_is_seeded_and_greedy_at_zero():
+    g = torch.Generator().manual_seed(0)
+    row = torch.randn(320, generator=g)
+    assert plain.plain_temperature_sample(row, 0.0, 1, 2) == int(row.argmax())
+    a = plain.plain_temperature_sample(row, 0.8, 1, 2)
+    assert a == plain.plain_temperature_sample(row, 0.8, 1, 2)
+    draws = {plain.plain_temperature_sample(row, 0.8, 1, p) for p in range(64)}
+    assert len(draws) > 4
+    u = plain.plain_uniform(3, 4, 1000)
+    assert 0 < u.min() and u.max() < 1 and abs(u.mean() - 0.5) < 0.05
