@@ -117,11 +117,12 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def model_folder() -> str:
+def model_folder(layers: int) -> str:
     """The random-weights model folder (written once per machine into the temporary folder)."""
     from distengine_b200.weights import write_random_model
+    MODEL["num_hidden_layers"] = layers
     folder = os.path.join(tempfile.gettempdir(), f"distengine_b200-bench-{os.getuid()}",
-                          "tinyllama-shape-seed0-bf16")
+                          f"tinyllama-shape-{layers}-layers-seed0-bf16")
     marker = os.path.join(folder, ".complete")
     if not os.path.isfile(marker):
         print("[bench] writing the random-weights model folder ...", file=sys.stderr, flush=True)
@@ -152,6 +153,11 @@ def main() -> int:
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
+                        help="measure one part only (small cases for profiling)")
+    parser.add_argument("--layers", type=int, default=MODEL["num_hidden_layers"],
+                        help="fewer layers than the configuration's 22, for small profiling runs")
+    parser.add_argument("--no-graphs", action="store_true")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -172,12 +178,13 @@ def main() -> int:
     from distengine_b200.kernels import ops
 
     peak, peak_kind = peaks()
-    folder = model_folder()
+    folder = model_folder(args.layers)
     rng = np.random.default_rng(0)
     vocab = MODEL["vocab_size"]
     pages = (64 * (PROMPT + 3 + 2 * NEW_TOKENS + steps) + PREFILL) // PAGE + 64
     engine = Engine(folder, EngineConfig(dtype="bfloat16", block_size=PAGE, num_blocks=pages,
-                                         decode_batch_size=64, max_batch_tokens=PREFILL))
+                                         decode_batch_size=64, max_batch_tokens=PREFILL,
+                                         use_graphs=not args.no_graphs))
     runner, model = engine.runner, engine.model
     w_bytes, layer_params = weight_bytes(model)
     kv_per_token = sum(2 * g.k.shape[0] * g.spec.kv_heads * g.spec.head_dim * g.k.element_size()
@@ -198,9 +205,12 @@ def main() -> int:
         runner.release("prefill")
         return start.elapsed_time(stop)
 
-    for _ in range(3):
-        prefill_once()
-    prefill_ms = statistics.median(prefill_once() for _ in range(5))
+    if args.only == "decode":
+        prefill_ms = float("nan")
+    else:
+        for _ in range(3):
+            prefill_once()
+        prefill_ms = statistics.median(prefill_once() for _ in range(5))
     cfg = model.config
     attn_flops = (4 * cfg.head_dim * cfg.num_attention_heads * PREFILL * (PREFILL + 1) // 2
                   * cfg.num_hidden_layers)
@@ -239,9 +249,19 @@ def main() -> int:
         runner.check_status()
         return ms, launches, context, (sampler.summary() if sampler else None)
 
+    if args.only == "prefill":
+        print(json.dumps({"impl": "ours", "only": "prefill", "layers": args.layers,
+                          "prefill": prefill}))
+        return 0
     ms, launches, context, clocks = decode(args.batch, steps, warmup, sample_clocks=True)
     step_bytes = w_bytes + args.batch * context * kv_per_token + args.batch * cfg.hidden_size * 2
     achieved = step_bytes / (ms * 1e-3) / 1e9
+    if args.only == "decode":
+        print(json.dumps({"impl": "ours", "only": "decode", "layers": args.layers,
+                          "batch": args.batch, "ms_per_step": round(ms, 4),
+                          "value": round(args.batch / ms * 1e3, 1), "gpu_launches": launches,
+                          "achieved_gbs": round(achieved, 1)}))
+        return 0
     points = {}
     for b in (1, 64):
         b_ms, _, _, _ = decode(b, min(steps, NEW_TOKENS), warmup)

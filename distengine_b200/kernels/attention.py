@@ -1,14 +1,30 @@
-"""Launches attention over the paged cache: picks the kernel for a dtype and head size, and runs
-a plan of work items (``attention_plan``) plus the merge of split key ranges."""
+"""Attention over the paged cache: picks the kernel for a dtype and head size, plans a step's work
+items on the host and launches them.
+
+* bfloat16 with a head size that is a multiple of 16: the tensor-core kernel
+  (``csrc/attention_mma.cu``, compiled for that head size at first use).  Sequences with many query
+  rows in the step use its wide tile (64 rows), sequences with at most 16 rows (decoded tokens)
+  its narrow tile (16 rows, the keys of a tile split over the warps).
+* float32, or any other even head size up to 256: the CUDA-core kernel in float32 arithmetic
+  (``csrc/attention_simt.cu``), 8 rows a tile.
+
+Long key ranges of a step with few tiles are cut into chunks; ``de_attn_combine`` merges the
+partial results (``attention_plan``).
+"""
 
 from __future__ import annotations
 
+from dataclasses import dataclass
+
+import numpy as np
 import torch
 
 from . import library
+from .attention_plan import build_plan, choose_chunk
 from .ops import _check, _i32, _need, _ptr, _stream, _tag
 
 MAX_HEAD_DIM = 256
+NARROW_ROWS = 16
 
 
 def check_head_dim(head_dim: int) -> None:
@@ -17,51 +33,146 @@ def check_head_dim(head_dim: int) -> None:
                          f"got {head_dim}")
 
 
-def rows_per_tile(dtype: torch.dtype, head_dim: int) -> int:
-    """Query rows in one work item of the kernel that serves this dtype and head size."""
-    check_head_dim(head_dim)
-    return 8
+def uses_tensor_cores(dtype: torch.dtype, head_dim: int) -> bool:
+    return dtype == torch.bfloat16 and head_dim % 16 == 0
 
 
-def paged_attention(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor,
-                    v_pages: torch.Tensor, block_table: torch.Tensor, seq_slot: torch.Tensor,
-                    seq_qstart: torch.Tensor, seq_qlen: torch.Tensor, seq_pos0: torch.Tensor,
-                    items: torch.Tensor, combine: "torch.Tensor | None", num_partials: int,
-                    tile_rows: int, partial_acc: "torch.Tensor | None",
-                    partial_ml: "torch.Tensor | None", heads: int, kv_heads: int, head_dim: int,
-                    scale: float, window: "int | None") -> None:
-    """q: [N, >= heads * d] rows (row stride free, heads first); out [N, heads * d]."""
-    check_head_dim(head_dim)
-    _need(q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == k_pages.dtype,
-          "paged_attention: q, out and the pages must share a dtype and have contiguous rows")
-    _need(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dim() == 4
-          and k_pages.shape[1] == kv_heads and k_pages.shape[3] == head_dim
-          and v_pages.shape == k_pages.shape,
-          "paged_attention: pages must be [pages, kv_heads, page, head_dim]")
-    _need(heads % kv_heads == 0, "paged_attention: heads must be a multiple of kv_heads")
-    for name, t in (("block_table", block_table), ("seq_slot", seq_slot),
-                    ("seq_qstart", seq_qstart), ("seq_qlen", seq_qlen), ("seq_pos0", seq_pos0),
-                    ("items", items)):
+@dataclass
+class _Shape:
+    name: str            # suffix of the step arrays of this tile shape
+    rows: int            # query rows in a tile
+    code: int            # the kernel's shape argument (-1: the CUDA-core kernel)
+
+
+class AttentionLauncher:
+    """Plans and runs the attention of all layers that share one shape of heads."""
+
+    def __init__(self, dtype: torch.dtype, heads: int, kv_heads: int, head_dim: int,
+                 scale: float, window: "int | None") -> None:
+        check_head_dim(head_dim)
+        if heads % kv_heads != 0:
+            raise ValueError(f"heads ({heads}) must be a multiple of kv_heads ({kv_heads})")
+        self.dtype, self.heads, self.kv_heads, self.head_dim = dtype, heads, kv_heads, head_dim
+        self.scale, self.window = float(scale), int(window or 0)
+        self.group = heads // kv_heads
+        self.tensor_cores = uses_tensor_cores(dtype, head_dim)
+        if self.tensor_cores:
+            self.shapes = [_Shape("wide", 64, 0), _Shape("narrow", NARROW_ROWS, 1)]
+            self.module = ("attention_mma", (f"HEAD_DIM={head_dim}",))
+        else:
+            self.shapes = [_Shape("rows8", 8, -1)]
+            self.module = ("attention_simt", ())
+        self.key = (f"attention/{'mma' if self.tensor_cores else 'simt'}/{self.group}/"
+                    f"{kv_heads}/{head_dim}/{self.window}")
+
+    def modules(self) -> list[tuple[str, tuple[str, ...]]]:
+        """The kernel libraries this launcher calls (to compile them side by side up front)."""
+        return [self.module, ("attention_simt", ())]
+
+    # ------------------------------------------------------------------ host side
+    def _split(self, seq_qlen: np.ndarray) -> list[np.ndarray]:
+        """The step's sequences divided over the tile shapes (zero rows where not taken)."""
+        if len(self.shapes) == 1:
+            return [seq_qlen]
+        narrow = seq_qlen.astype(np.int64) * self.group <= NARROW_ROWS
+        # with many query heads per kv head even one token fills more than a narrow tile; such
+        # sequences still take narrow tiles while they bring a single token
+        narrow |= seq_qlen == 1
+        return [np.where(narrow, 0, seq_qlen).astype(np.int32),
+                np.where(narrow, seq_qlen, 0).astype(np.int32)]
+
+    def prepare(self, prep, force_chunk: "int | None" = None,
+                force_cap: "int | None" = None, force_shape: "str | None" = None) -> None:
+        """Add this step's work lists to ``prep`` (once per step for all layers of this shape).
+        The ``force_*`` arguments pin the chunk size, the chunk cap and the tile shape; tests use
+        them to reach every path at small sizes."""
+        if self.key in prep.notes:
+            return
+        host = prep.host
+        notes = {}
+        parts = self._split(host.seq_qlen)
+        if force_shape is not None:
+            parts = [host.seq_qlen if s.name == force_shape else np.zeros_like(host.seq_qlen)
+                     for s in self.shapes]
+        total_tiles = sum(int(((q.astype(np.int64) * self.group + s.rows - 1) // s.rows).sum())
+                          for q, s in zip(parts, self.shapes))
+        for qlen, shape in zip(parts, self.shapes):
+            chunk = chunks_cap = None
+            if force_chunk is not None:
+                chunk, chunks_cap = force_chunk, force_cap
+            elif prep.graph_shape is not None:
+                cap = int(prep.graph_shape["context_cap"])
+                span = cap if not self.window else min(cap, self.window + int(host.seq_qlen.max()))
+                chunk = choose_chunk(total_tiles, self.kv_heads, span)
+                if chunk:
+                    chunks_cap = (span + chunk - 1) // chunk + (1 if self.window else 0)
+            elif int(qlen.sum()):
+                live = qlen > 0
+                longest = int((host.seq_pos0[live] + qlen[live]).max())
+                if self.window:
+                    longest = min(longest, self.window + int(qlen.max()))
+                chunk = choose_chunk(total_tiles, self.kv_heads, longest)
+            plan = build_plan(qlen, host.seq_pos0, self.group, self.kv_heads, shape.rows,
+                              self.window, chunk, chunks_cap)
+            prep.add(f"{self.key}/{shape.name}/items", plan.items)
+            prep.add(f"{self.key}/{shape.name}/combine", plan.combine)
+            notes[shape.name] = plan.num_partials
+        prep.notes[self.key] = tuple(sorted(notes.items()))
+
+    # ------------------------------------------------------------------ device side
+    def run(self, q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor,
+            v_pages: torch.Tensor, block_table: torch.Tensor, ctx) -> None:
+        """q: rows of [heads * d] query features at the front of each row of ``q`` (row stride
+        free); out [N, heads * d]; keys and values [pages, kv_heads, page, d]."""
+        d = self.head_dim
+        _need(q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == k_pages.dtype
+              == self.dtype, "paged attention: q, out and the pages must have the layer's dtype "
+              "and contiguous rows")
+        _need(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dim() == 4
+              and k_pages.shape[1] == self.kv_heads and k_pages.shape[3] == d
+              and v_pages.shape == k_pages.shape,
+              "paged attention: pages must be [pages, kv_heads, page, head_dim]")
+        _i32(block_table, "block_table")
+        partials = dict(ctx.notes[self.key])
+        for shape in self.shapes:
+            items = ctx.arrays[f"{self.key}/{shape.name}/items"]
+            combine = ctx.arrays[f"{self.key}/{shape.name}/combine"]
+            if items.shape[0] == 0:
+                continue
+            num_partials = partials[shape.name]
+            acc = ml = None
+            if num_partials:
+                rows = num_partials * self.kv_heads * shape.rows
+                acc = ctx.buffer(f"attention.partial_acc.{shape.name}", (rows * d,), torch.float32)
+                ml = ctx.buffer(f"attention.partial_ml.{shape.name}", (rows * 2,), torch.float32)
+            launch_items(shape.code, self.module, q, out, k_pages, v_pages, block_table,
+                         ctx.seq_slot, ctx.seq_qstart, ctx.seq_qlen, ctx.seq_pos0, items, combine,
+                         shape.rows, acc, ml, self.heads, self.kv_heads, d, self.scale, self.window)
+
+
+def launch_items(code: int, module, q, out, k_pages, v_pages, block_table, seq_slot, seq_qstart,
+                 seq_qlen, seq_pos0, items, combine, tile_rows, partial_acc, partial_ml, heads,
+                 kv_heads, head_dim, scale, window) -> None:
+    """One launch of a kernel over ``items`` and, if any range was split, the merge."""
+    for name, t in (("seq_slot", seq_slot), ("seq_qstart", seq_qstart), ("seq_qlen", seq_qlen),
+                    ("seq_pos0", seq_pos0), ("items", items)):
         _i32(t, name)
-    num_items = items.shape[0]
-    if num_partials > 0:
-        need = num_partials * kv_heads * tile_rows
-        _need(partial_acc is not None and partial_ml is not None
-              and partial_acc.dtype == torch.float32 and partial_ml.dtype == torch.float32
-              and partial_acc.numel() >= need * head_dim and partial_ml.numel() >= need * 2,
-              "paged_attention: scratch for partial results is too small")
-    lib = library.load("attention_simt")
-    _check(lib.de_attn_simt(_tag(q.dtype), q.data_ptr(), q.stride(0), out.data_ptr(),
-                            out.stride(0), k_pages.data_ptr(), v_pages.data_ptr(),
-                            block_table.data_ptr(), block_table.stride(0), k_pages.shape[0],
-                            seq_slot.data_ptr(), seq_qstart.data_ptr(), seq_qlen.data_ptr(),
-                            seq_pos0.data_ptr(), items.data_ptr(), num_items, _ptr(partial_acc),
-                            _ptr(partial_ml), heads, kv_heads, head_dim, k_pages.shape[2],
-                            float(scale), int(window or 0), _stream()), "paged_attention")
+    lib = library.load(*module)
+    common = (q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), k_pages.data_ptr(),
+              v_pages.data_ptr(), block_table.data_ptr(), block_table.stride(0),
+              k_pages.shape[0], seq_slot.data_ptr(), seq_qstart.data_ptr(), seq_qlen.data_ptr(),
+              seq_pos0.data_ptr(), items.data_ptr(), items.shape[0], _ptr(partial_acc),
+              _ptr(partial_ml), heads, kv_heads, head_dim, k_pages.shape[2], float(scale),
+              int(window or 0), _stream())
+    if code < 0:
+        _check(lib.de_attn_simt(_tag(q.dtype), *common), "paged attention")
+    else:
+        _check(lib.de_attn_mma(code, *common), "paged attention (tensor cores)")
     if combine is not None and combine.shape[0] > 0:
         _i32(combine, "combine")
-        _check(lib.de_attn_combine(_tag(q.dtype), out.data_ptr(), out.stride(0),
-                                   seq_qstart.data_ptr(), seq_qlen.data_ptr(), combine.data_ptr(),
-                                   combine.shape[0], partial_acc.data_ptr(), partial_ml.data_ptr(),
-                                   heads, kv_heads, head_dim, tile_rows, _stream()),
-               "attention combine")
+        merge = library.load("attention_simt")
+        _check(merge.de_attn_combine(_tag(q.dtype), out.data_ptr(), out.stride(0),
+                                     seq_qstart.data_ptr(), seq_qlen.data_ptr(),
+                                     combine.data_ptr(), combine.shape[0], partial_acc.data_ptr(),
+                                     partial_ml.data_ptr(), heads, kv_heads, head_dim, tile_rows,
+                                     _stream()), "attention combine")

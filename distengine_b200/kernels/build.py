@@ -32,6 +32,7 @@ MODULES: dict[str, tuple[str, tuple[str, ...]]] = {
     "core": ("core.cu", ()),
     "gemm_f32": ("gemm_f32.cu", ()),
     "attention_simt": ("attention_simt.cu", ()),
+    "attention_mma": ("attention_mma.cu", ()),          # built per head size: HEAD_DIM=<d>
 }
 
 

@@ -36,13 +36,20 @@ SIGNATURES: dict[str, dict[str, list]] = {
         "de_attn_simt": [I, P, I, P, I, P, P, P, I, I, P, P, P, P, P, I, P, P, I, I, I, I, F, I, P],
         "de_attn_combine": [I, P, I, P, P, P, I, P, P, I, I, I, I, P],
     },
+    "attention_mma": {
+        "de_attn_mma_head_dim": [],
+        "de_attn_mma": [I, P, I, P, I, P, P, P, I, I, P, P, P, P, P, I, P, P, I, I, I, I, F, I, P],
+    },
 }
 
 _loaded: dict[tuple[str, tuple[str, ...]], ctypes.CDLL] = {}
 
 
 def default_build_requests() -> list[tuple[str, tuple[str, ...]]]:
-    return [(module, ()) for module in _build.MODULES if module in SIGNATURES]
+    """Every module; the per-head-size attention for the head sizes of common models."""
+    requests = [(module, ()) for module in _build.MODULES
+                if module in SIGNATURES and module != "attention_mma"]
+    return requests + [("attention_mma", (f"HEAD_DIM={d}",)) for d in (64, 128)]
 
 
 def load(module: str, defines: tuple[str, ...] = ()) -> ctypes.CDLL:

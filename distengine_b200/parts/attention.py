@@ -12,9 +12,8 @@ from __future__ import annotations
 import torch
 
 from ..config.model import PartSpec
-from ..kernels import attention as attention_kernels
 from ..kernels import ops
-from ..kernels.attention_plan import build_plan, choose_chunk
+from ..kernels.attention import AttentionLauncher
 from .base import (Mixer, PagedKVSpec, build_position_encoding, compute_matrix, register_mixer)
 from .context import CacheBinding, StepContext, StepPrep
 
@@ -29,14 +28,12 @@ class PagedAttention(Mixer):
                              f"({kv_heads})")            # src/layers/attention.py:18-19
         if window is not None and window <= 0:
             raise ValueError(f"attention: window must be positive or None, got {window}")
-        attention_kernels.check_head_dim(head_dim)
         self.width, self.heads, self.kv_heads, self.head_dim = width, heads, kv_heads, head_dim
         self.scale, self.window = float(scale), window
         self.position = build_position_encoding(position, dtype, device)
-        self.tile_rows = attention_kernels.rows_per_tile(dtype, head_dim)
+        self.kernels = AttentionLauncher(dtype, heads, kv_heads, head_dim, scale, window)
         self.w_qkv: "torch.Tensor | None" = None
         self.w_o: "torch.Tensor | None" = None
-        self._key = f"attention/{heads // kv_heads}/{kv_heads}/{self.tile_rows}/{window or 0}"
 
     # ------------------------------------------------------------------ weights
     def tensors(self):
@@ -58,24 +55,7 @@ class PagedAttention(Mixer):
 
     # ------------------------------------------------------------------ step
     def prepare(self, prep: StepPrep) -> None:
-        if prep.has(self._key + "/items"):
-            return                                   # a layer of the same shape planned already
-        host = prep.host
-        group = self.heads // self.kv_heads
-        chunk = chunks_cap = None
-        if prep.graph_shape is not None:
-            cap = int(prep.graph_shape["context_cap"])
-            tiles = int(((host.seq_qlen.astype("int64") * group + self.tile_rows - 1)
-                         // self.tile_rows).sum())
-            span = cap if self.window is None else min(cap, self.window + int(host.seq_qlen.max()))
-            chunk = choose_chunk(tiles, self.kv_heads, span)
-            if chunk:
-                chunks_cap = (span + chunk - 1) // chunk + (0 if self.window is None else 1)
-        plan = build_plan(host.seq_qlen, host.seq_pos0, group, self.kv_heads, self.tile_rows,
-                          self.window or 0, chunk, chunks_cap)
-        prep.add(self._key + "/items", plan.items)
-        prep.add(self._key + "/combine", plan.combine)
-        prep.notes[self._key] = plan.num_partials
+        self.kernels.prepare(prep)
 
     def forward(self, x: torch.Tensor, ctx: StepContext,
                 cache: "CacheBinding | None") -> torch.Tensor:
@@ -92,17 +72,7 @@ class PagedAttention(Mixer):
                           self.kv_heads, d, cache.k_pages, cache.v_pages, cache.block_table,
                           cache.writes, ctx.status)
         out = ctx.buffer("attention.context", (n, self.heads * d))
-        num_partials = ctx.notes[self._key]
-        acc = ml = None
-        if num_partials:
-            rows = num_partials * self.kv_heads * self.tile_rows
-            acc = ctx.buffer("attention.partial_acc", (rows * d,), torch.float32)
-            ml = ctx.buffer("attention.partial_ml", (rows * 2,), torch.float32)
-        attention_kernels.paged_attention(
-            qkv, out, cache.k_pages, cache.v_pages, cache.block_table, ctx.seq_slot,
-            ctx.seq_qstart, ctx.seq_qlen, ctx.seq_pos0, ctx.arrays[self._key + "/items"],
-            ctx.arrays[self._key + "/combine"], num_partials, self.tile_rows, acc, ml,
-            self.heads, self.kv_heads, d, self.scale, self.window)
+        self.kernels.run(qkv, out, cache.k_pages, cache.v_pages, cache.block_table, ctx)
         branch = ctx.buffer("attention.out", (n, self.width))
         ops.linear(out, self.w_o, out=branch)
         return branch

@@ -81,18 +81,22 @@ class PagedFixture:
 
 
 def run_paged_attention(fx: PagedFixture, q_list, heads, kv_heads, head_dim, scale, window,
-                        chunk=None, chunks_cap=None):
+                        chunk=None, chunks_cap=None, shape=None):
     """q_list[i]: [q_len_i, heads, d] float32 queries of the LAST q_len_i positions of sequence i.
-    Returns the kernel's output [N, heads*d] float32 (on the CPU)."""
-    from distengine_b200.kernels import attention as ak
-    from distengine_b200.kernels.attention_plan import build_plan
+    Runs the engine's own launcher (``kernels.attention.AttentionLauncher``): ``chunk`` /
+    ``chunks_cap`` pin how key ranges are split (0: not at all, None: the launcher's choice),
+    ``shape`` pins the tile shape.  Returns the output [N, heads*d] float32 on the CPU and the
+    number of partial results per tile shape."""
+    from types import SimpleNamespace
+    from distengine_b200.kernels.attention import AttentionLauncher
+    from distengine_b200.parts.context import StepPrep, Workspace
     dev, dtype = fx.device, fx.dtype
     qlen = np.array([q.shape[0] for q in q_list], dtype=np.int32)
     pos0 = np.array([n - ql for n, ql in zip(fx.kv_lens, qlen)], dtype=np.int32)
     qstart = (np.cumsum(qlen) - qlen).astype(np.int32)
-    rows = ak.rows_per_tile(dtype, head_dim)
-    plan = build_plan(qlen, pos0, heads // kv_heads, kv_heads, rows, window or 0, chunk,
-                      chunks_cap)
+    launcher = AttentionLauncher(dtype, heads, kv_heads, head_dim, scale, window)
+    prep = StepPrep(SimpleNamespace(seq_qlen=qlen, seq_pos0=pos0))
+    launcher.prepare(prep, force_chunk=chunk, force_cap=chunks_cap, force_shape=shape)
     q = torch.cat([t.reshape(t.shape[0], heads * head_dim) for t in q_list]).to(dev, dtype)
     # q lives inside a wider row, as in the engine's fused qkv buffer
     wide = torch.zeros(q.shape[0], heads * head_dim + 2 * kv_heads * head_dim, dtype=dtype,
@@ -101,16 +105,14 @@ def run_paged_attention(fx: PagedFixture, q_list, heads, kv_heads, head_dim, sca
     out = torch.full((q.shape[0], heads * head_dim), float("nan"), dtype=dtype, device=dev)
     k_pages, v_pages, table = fx.to_device()
     t = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(dev)
-    acc = ml = None
-    if plan.num_partials:
-        n = plan.num_partials * kv_heads * rows
-        acc = torch.full((n * head_dim,), float("nan"), dtype=torch.float32, device=dev)
-        ml = torch.full((n * 2,), float("nan"), dtype=torch.float32, device=dev)
-    ak.paged_attention(wide, out, k_pages, v_pages, table, t(np.array(fx.slots)), t(qstart),
-                       t(qlen), t(pos0), t(plan.items), t(plan.combine), plan.num_partials, rows,
-                       acc, ml, heads, kv_heads, head_dim, scale, window)
+    workspace = Workspace(torch.device(dev))
+    ctx = SimpleNamespace(seq_slot=t(np.array(fx.slots)), seq_qstart=t(qstart), seq_qlen=t(qlen),
+                          seq_pos0=t(pos0), notes=prep.notes,
+                          arrays={k: t(v) for k, v in prep.extra.items()},
+                          buffer=lambda name, shape, dt=None: workspace.get(name, shape, dt or dtype))
+    launcher.run(wide, out, k_pages, v_pages, table, ctx)
     torch.cuda.synchronize()
-    return out.float().cpu(), plan
+    return out.float().cpu(), dict(prep.notes[launcher.key])
 
 
 class PartHarness:

@@ -234,10 +234,17 @@ def _plain_attention_case(fx, q_list, heads, kv_heads, d, scale, window, dtype):
     return torch.cat(outs)
 
 
+def _shapes(dtype, d):
+    """The tile shapes to force: the launcher's own choice, and each shape of its kernel alone."""
+    from distengine_b200.kernels.attention import uses_tensor_cores
+    return [None, "wide", "narrow"] if uses_tensor_cores(dtype, d) else [None]
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads,kv_heads,d,page", [(4, 2, 16, 16), (3, 3, 32, 8), (6, 1, 48, 32),
                                                    (8, 1, 64, 16), (5, 5, 80, 4), (16, 2, 128, 64),
-                                                   (2, 1, 256, 16), (32, 4, 64, 16)])
+                                                   (2, 1, 256, 16), (32, 4, 64, 16), (3, 1, 18, 16),
+                                                   (32, 1, 64, 16)])
 def test_paged_attention_mixed_batch(dtype, heads, kv_heads, d, page):
     """Prompt portions beside decoded tokens, scrambled block tables, NaN in every free page."""
     g = torch.Generator().manual_seed(heads * d + page)
@@ -247,19 +254,22 @@ def test_paged_attention_mixed_batch(dtype, heads, kv_heads, d, page):
     q_list = [torch.randn(ql, heads, d, generator=g).to(dtype).float() for ql in q_lens]
     scale = d ** -0.5
     want = _plain_attention_case(fx, q_list, heads, kv_heads, d, scale, None, dtype)
-    got, plan = run_paged_attention(fx, q_list, heads, kv_heads, d, scale, None, chunk=0)
-    assert plan.num_partials == 0
-    assert_close(got, want, dtype, "paged attention")
-    got, plan = run_paged_attention(fx, q_list, heads, kv_heads, d, scale, None)
-    assert_close(got, want, dtype, "paged attention, chunk chosen by the plan")
-    # the same with every key range cut into chunks of 64 and merged
-    got, plan = run_paged_attention(fx, q_list, heads, kv_heads, d, scale, None, chunk=64)
-    assert plan.num_partials > 0
-    assert_close(got, want, dtype, "paged attention, split keys")
-    # and with the fixed-shape plan that a replayed graph uses
-    got, plan = run_paged_attention(fx, q_list, heads, kv_heads, d, scale, None, chunk=128,
-                                    chunks_cap=4)
-    assert_close(got, want, dtype, "paged attention, capped chunks")
+    for shape in _shapes(dtype, d):
+        got, partials = run_paged_attention(fx, q_list, heads, kv_heads, d, scale, None, chunk=0,
+                                            shape=shape)
+        assert sum(partials.values()) == 0
+        assert_close(got, want, dtype, f"paged attention {shape}")
+        got, _ = run_paged_attention(fx, q_list, heads, kv_heads, d, scale, None, shape=shape)
+        assert_close(got, want, dtype, f"paged attention, chunk chosen by the plan {shape}")
+        # the same with every key range cut into chunks of 64 and merged
+        got, partials = run_paged_attention(fx, q_list, heads, kv_heads, d, scale, None, chunk=64,
+                                            shape=shape)
+        assert sum(partials.values()) > 0
+        assert_close(got, want, dtype, f"paged attention, split keys {shape}")
+        # and with the fixed-shape plan that a replayed graph uses
+        got, _ = run_paged_attention(fx, q_list, heads, kv_heads, d, scale, None, chunk=128,
+                                     chunks_cap=4, shape=shape)
+        assert_close(got, want, dtype, f"paged attention, capped chunks {shape}")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -277,15 +287,19 @@ def test_paged_attention_window(dtype, d, page, window):
     fx.k[0][edge] = q_list[0][0, :kv_heads] * 2
     fx.rewrite()
     want = _plain_attention_case(fx, q_list, heads, kv_heads, d, d ** -0.5, window, dtype)
-    for chunk in (0, None, 64):
-        got, _ = run_paged_attention(fx, q_list, heads, kv_heads, d, d ** -0.5, window, chunk=chunk)
-        assert_close(got, want, dtype, f"windowed attention chunk={chunk}")
+    for shape in _shapes(dtype, d):
+        for chunk in (0, None, 64):
+            got, _ = run_paged_attention(fx, q_list, heads, kv_heads, d, d ** -0.5, window,
+                                         chunk=chunk, shape=shape)
+            assert_close(got, want, dtype, f"windowed attention chunk={chunk} {shape}")
     # pages wholly behind the window may be gone from the table: same result
     first_kept = (kv_lens[0] - window + 1) // page
     for p in range(first_kept):
         fx.block_table[fx.slots[0], p] = -1
-    got, _ = run_paged_attention(fx, q_list, heads, kv_heads, d, d ** -0.5, window, chunk=0)
-    assert_close(got, want, dtype, "windowed attention, released pages")
+    for shape in _shapes(dtype, d):
+        got, _ = run_paged_attention(fx, q_list, heads, kv_heads, d, d ** -0.5, window, chunk=0,
+                                     shape=shape)
+        assert_close(got, want, dtype, f"windowed attention, released pages {shape}")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -297,11 +311,23 @@ def test_paged_attention_one_far_key_stands_out(dtype, far):
     g = torch.Generator().manual_seed(far)
     fx = PagedFixture([1101], kv_heads, d, page, dtype, DEV, seed=far)
     q = torch.randn(1, heads, d, generator=g).to(dtype).float()
-    q[0, 5] = q[0, 5] / q[0, 5].norm() * 8
+    q[0, 5] = (q[0, 5] / q[0, 5].norm() * 8).to(dtype).float()
     fx.k[0][far, 1] = (q[0, 5] * 4).to(dtype).float()         # head 5 reads kv head 1
     fx.rewrite()
     want = _plain_attention_case(fx, [q], heads, kv_heads, d, d ** -0.5, None, dtype)
     assert torch.allclose(want[0, 5 * d: 6 * d], fx.v[0][far, 1], atol=2e-2)
-    for chunk in (0, 256):
-        got, _ = run_paged_attention(fx, [q], heads, kv_heads, d, d ** -0.5, None, chunk=chunk)
-        assert_close(got, want, dtype, f"far key {far} chunk={chunk}")
+    for shape in _shapes(dtype, d):
+        for chunk in (0, 256):
+            got, _ = run_paged_attention(fx, [q], heads, kv_heads, d, d ** -0.5, None, chunk=chunk,
+                                         shape=shape)
+            assert_close(got, want, dtype, f"far key {far} chunk={chunk} {shape}")
+
+
+def test_attention_refuses_sizes_it_does_not_take():
+    from distengine_b200.kernels.attention import AttentionLauncher
+    with pytest.raises(ValueError, match="head sizes"):
+        AttentionLauncher(torch.bfloat16, 4, 2, 257, 1.0, None)
+    with pytest.raises(ValueError, match="head sizes"):
+        AttentionLauncher(torch.float32, 4, 2, 33, 1.0, None)
+    with pytest.raises(ValueError, match="multiple"):
+        AttentionLauncher(torch.float32, 5, 2, 32, 1.0, None)
