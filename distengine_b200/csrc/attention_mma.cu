@@ -19,6 +19,8 @@
 
 #include "common.cuh"
 
+DE_DEFINE_PDL_SWITCH
+
 #ifndef HEAD_DIM
 #define HEAD_DIM 64
 #endif
@@ -95,7 +97,10 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16
     __nv_bfloat16* v_s = k_s + 2 * KT * LDS;                                  // [2][KT][LDS]
 
     const WorkItem it = items[blockIdx.x];
-    if (it.kv_begin >= it.kv_end) return;                                     // padding item
+    if (it.kv_begin >= it.kv_end) {                                           // padding item
+        pdl_wait();
+        return;
+    }
     const int hk = blockIdx.y;
     const int g = heads / kv_heads;
     const int qlen = seq_qlen[it.seq], pos0 = seq_pos0[it.seq];
@@ -116,6 +121,8 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16
         hq[i] = hk * g + (live[i] ? row[i] % g : 0);
         pos[i] = live[i] ? pos0 + tok[i] : -1;
     }
+
+    pdl_wait();            // q, and the keys and values of this step's tokens, are just written
 
     // q fragments straight from global memory (read once)
     unsigned qf[D / 16][4];
@@ -273,6 +280,7 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16
         __syncthreads();                       // this stage may be overwritten by the next load
     }
     cp_async_wait<0>();
+    pdl_trigger();
 
     // row sums live in the 4 lanes of a quad
 #pragma unroll
@@ -375,12 +383,11 @@ int launch(const void* q, int q_stride, void* out, int out_stride, const void* k
         if (e != cudaSuccess) return (int)e;
     }
     dim3 grid(num_items, kv_heads);
-    kernel<<<grid, THREADS, smem, s>>>(
-        (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride,
-        (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table, table_stride,
-        num_pages, seq_slot, seq_qstart, seq_qlen, seq_pos0, (const WorkItem*)items, partial_acc,
-        partial_ml, heads, kv_heads, page, scale, window);
-    return de_check(cudaGetLastError());
+    return de_launch(kernel, grid, dim3(THREADS), smem, s, (const __nv_bfloat16*)q, q_stride,
+                     (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pages,
+                     (const __nv_bfloat16*)v_pages, block_table, table_stride, num_pages, seq_slot,
+                     seq_qstart, seq_qlen, seq_pos0, (const WorkItem*)items, partial_acc,
+                     partial_ml, heads, kv_heads, page, scale, window);
 }
 
 }  // namespace

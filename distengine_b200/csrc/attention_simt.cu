@@ -19,6 +19,8 @@
 
 #include "common.cuh"
 
+DE_DEFINE_PDL_SWITCH
+
 namespace {
 
 constexpr int ROWS = 8;        // query rows (warps) per block
@@ -53,7 +55,10 @@ attn_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int
     float* Qs = Vs + TILE * d;              // [ROWS][d]
 
     const WorkItem it = items[blockIdx.x];
-    if (it.kv_begin >= it.kv_end) return;   // padding item
+    if (it.kv_begin >= it.kv_end) {         // padding item
+        pdl_wait();
+        return;
+    }
     const int hk = blockIdx.y;
     const int g = heads / kv_heads;
     const int qlen = seq_qlen[it.seq], pos0 = seq_pos0[it.seq];
@@ -67,6 +72,7 @@ attn_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int
     const int hq = hk * g + (active ? r % g : 0);
     const int pos = pos0 + t;
 
+    pdl_wait();            // q, and the keys and values of this step's tokens, are just written
     for (int i = lane; i < d; i += 32)
         Qs[warp * d + i] = active ? to_float(q[(size_t)(tok0 + t) * q_stride + hq * d + i]) : 0.0f;
 
@@ -135,6 +141,7 @@ attn_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int
         }
         m = m_new;
     }
+    pdl_trigger();
     if (!active) return;
 
     if (it.partial < 0) {
@@ -168,6 +175,8 @@ attn_combine_kernel(T* __restrict__ out, int out_stride, const int* __restrict__
                     const float* __restrict__ partial_acc, const float* __restrict__ partial_ml,
                     int heads, int kv_heads, int d, int rows_per_tile) {
     const CombineItem it = items[blockIdx.x];
+    pdl_wait();
+    pdl_trigger();
     if (it.num_partials <= 0) return;
     const int hk = blockIdx.y;
     const int g = heads / kv_heads;
@@ -233,16 +242,15 @@ DE_EXPORT int de_attn_simt(int dtype, const void* q, int q_stride, void* out, in
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
             if (e != cudaSuccess) return (int)e;                                                \
         }                                                                                       \
-        attn_simt_kernel<T><<<grid, ROWS * 32, smem, s>>>(                                      \
-            (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pages, (const T*)v_pages,   \
-            block_table, table_stride, num_pages, seq_slot, seq_qstart, seq_qlen, seq_pos0,     \
-            (const WorkItem*)items, partial_acc, partial_ml, heads, kv_heads, d, page, scale,   \
-            window);                                                                            \
+        return de_launch(attn_simt_kernel<T>, grid, dim3(ROWS * 32), smem, s, (const T*)q,      \
+                         q_stride, (T*)out, out_stride, (const T*)k_pages, (const T*)v_pages,   \
+                         block_table, table_stride, num_pages, seq_slot, seq_qstart, seq_qlen,  \
+                         seq_pos0, (const WorkItem*)items, partial_acc, partial_ml, heads,      \
+                         kv_heads, d, page, scale, window);                                     \
     } while (0)
     if (dtype == DE_BF16) LAUNCH(__nv_bfloat16);
-    else LAUNCH(float);
+    LAUNCH(float);
 #undef LAUNCH
-    return de_check(cudaGetLastError());
 }
 
 // `rows_per_tile`: rows of a tile in the partial layout (8 for the kernel above; the tensor-core
@@ -256,12 +264,11 @@ DE_EXPORT int de_attn_combine(int dtype, void* out, int out_stride, const int* s
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(num_items, kv_heads);
     if (dtype == DE_BF16)
-        attn_combine_kernel<__nv_bfloat16><<<grid, ROWS * 32, 0, s>>>(
-            (__nv_bfloat16*)out, out_stride, seq_qstart, seq_qlen, (const CombineItem*)items,
-            partial_acc, partial_ml, heads, kv_heads, d, rows_per_tile);
-    else
-        attn_combine_kernel<float><<<grid, ROWS * 32, 0, s>>>(
-            (float*)out, out_stride, seq_qstart, seq_qlen, (const CombineItem*)items, partial_acc,
-            partial_ml, heads, kv_heads, d, rows_per_tile);
-    return de_check(cudaGetLastError());
+        return de_launch(attn_combine_kernel<__nv_bfloat16>, grid, dim3(ROWS * 32), 0, s,
+                         (__nv_bfloat16*)out, out_stride, seq_qstart, seq_qlen,
+                         (const CombineItem*)items, partial_acc, partial_ml, heads, kv_heads, d,
+                         rows_per_tile);
+    return de_launch(attn_combine_kernel<float>, grid, dim3(ROWS * 32), 0, s, (float*)out,
+                     out_stride, seq_qstart, seq_qlen, (const CombineItem*)items, partial_acc,
+                     partial_ml, heads, kv_heads, d, rows_per_tile);
 }

@@ -54,3 +54,41 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* 33 floats 
 }
 
 static inline int de_check(cudaError_t e) { return e == cudaSuccess ? 0 : (int)e; }
+
+// ---------------------------------------------------------------------------------------------
+// Programmatic dependent launch: the launch of a kernel overlaps the tail of the kernel before it
+// in the stream.  A kernel calls pdl_wait() before its first access to memory that another kernel
+// of the step writes (or reads while this one writes); it returns once the preceding kernel has
+// completed and its writes are visible.  Before that a kernel may only do index arithmetic and read
+// weights and the step's arrays, which no kernel writes.  pdl_trigger() tells the scheduler that
+// the next kernel may be launched; kernels call it when their main loop is done, before they write
+// their outputs (measured on B200: triggering at the start of every kernel made decode steps 10%
+// slower than no overlap at all, triggering late makes them 3% faster).  Every kernel calls
+// pdl_wait() on all paths, so completion is transitive along the stream.  Without the launch
+// attribute both calls do nothing.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_trigger() {
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+
+static int g_pdl = 1;          // per library; de_set_pdl switches it
+
+template <typename... KArgs, typename... Args>
+static inline int de_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                            cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_pdl ? 1 : 0;
+    return de_check(cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...));
+}
+
+#define DE_DEFINE_PDL_SWITCH \
+    DE_EXPORT int de_set_pdl(int on) { g_pdl = on ? 1 : 0; return 0; }

@@ -10,6 +10,8 @@
 
 #include "common.cuh"
 
+DE_DEFINE_PDL_SWITCH
+
 // ------------------------------------------------------------------------------------------
 // embedding: out[n, :] = float(table[ids[n], :])           (the residual stream starts here)
 // ------------------------------------------------------------------------------------------
@@ -21,6 +23,8 @@ __global__ void embed_rows_kernel(const int* __restrict__ ids, const T* __restri
     if (id < 0 || id >= vocab) id = 0;          // ids are validated on the host; never read outside
     const T* row = table + (size_t)id * width;
     float* dst = out + (size_t)n * width;
+    pdl_wait();                                  // the last step's kernels may still read `out`
+    pdl_trigger();
     for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = to_float(row[i]);
 }
 
@@ -30,11 +34,10 @@ DE_EXPORT int de_embed_rows(int dtype, const int* ids, const void* table, float*
     const int threads = width >= 1024 ? 256 : 128;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == DE_BF16)
-        embed_rows_kernel<__nv_bfloat16><<<n, threads, 0, s>>>(ids, (const __nv_bfloat16*)table,
-                                                               out, width, vocab);
-    else
-        embed_rows_kernel<float><<<n, threads, 0, s>>>(ids, (const float*)table, out, width, vocab);
-    return de_check(cudaGetLastError());
+        return de_launch(embed_rows_kernel<__nv_bfloat16>, dim3(n), dim3(threads), 0, s, ids,
+                         (const __nv_bfloat16*)table, out, width, vocab);
+    return de_launch(embed_rows_kernel<float>, dim3(n), dim3(threads), 0, s, ids,
+                     (const float*)table, out, width, vocab);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -55,6 +58,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restric
     float* r = resid + (size_t)row * width;
     const T* d = delta ? delta + (size_t)row * width : nullptr;
     const bool update = (rows == nullptr) && (delta != nullptr);
+    pdl_wait();
 
     float ss = 0.0f;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
@@ -64,6 +68,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restric
         ss += x * x;
     }
     const float total = block_sum(ss, scratch);
+    pdl_trigger();
     const float inv = rsqrtf(total / (float)width + eps);
     T* o = out + (size_t)i_out * width;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
@@ -74,24 +79,129 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restric
     }
 }
 
+// four consecutive elements as one load or store
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+    static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
+        const float4 t = *reinterpret_cast<const float4*>(p);
+        v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float (&v)[4]) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+};
+template <> struct Vec4<__nv_bfloat16> {
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[4]) {
+        const uint2 t = *reinterpret_cast<const uint2*>(p);
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&t.x);
+        const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&t.y);
+        v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[4]) {
+        const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]);
+        const __nv_bfloat162 b = __floats2bfloat162_rn(v[2], v[3]);
+        uint2 t;
+        t.x = *reinterpret_cast<const unsigned*>(&a);
+        t.y = *reinterpret_cast<const unsigned*>(&b);
+        *reinterpret_cast<uint2*>(p) = t;
+    }
+};
+
+// The same for widths that are a multiple of 4 and at most 4 * CHUNKS * blockDim: the row stays in
+// registers between the sum of squares and the scaling, every access is 8 or 16 bytes wide.
+template <typename T, typename W, int CHUNKS>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __restrict__ delta,
+                                       const W* __restrict__ weight, T* __restrict__ out,
+                                       const int* __restrict__ rows, int width, float eps) {
+    __shared__ float scratch[33];
+    const int i_out = blockIdx.x;
+    const int row = rows ? rows[i_out] : i_out;
+    float* r = resid + (size_t)row * width;
+    const T* d = delta ? delta + (size_t)row * width : nullptr;
+    const bool update = (rows == nullptr) && (delta != nullptr);
+    const int quads = width >> 2;
+
+    float wv[CHUNKS][4];
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {               // the weight is no kernel's output
+        const int qd = threadIdx.x + c * blockDim.x;
+        if (qd < quads) Vec4<W>::load(weight + 4 * qd, wv[c]);
+    }
+    pdl_wait();
+
+    float x[CHUNKS][4];
+    float ss = 0.0f;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+        const int qd = threadIdx.x + c * blockDim.x;
+        if (qd < quads) {
+            Vec4<float>::load(r + 4 * qd, x[c]);
+            if (d) {
+                float dv[4];
+                Vec4<T>::load(d + 4 * qd, dv);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) x[c][e] += dv[e];
+            }
+            if (update) Vec4<float>::store(r + 4 * qd, x[c]);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) ss += x[c][e] * x[c][e];
+        }
+    }
+    const float total = block_sum(ss, scratch);
+    pdl_trigger();
+    const float inv = rsqrtf(total / (float)width + eps);
+    T* o = out + (size_t)i_out * width;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+        const int qd = threadIdx.x + c * blockDim.x;
+        if (qd < quads) {
+            float y[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                y[e] = to_float(from_float<T>(x[c][e] * inv)) * wv[c][e];
+            Vec4<T>::store(o + 4 * qd, y);
+        }
+    }
+}
+
+template <typename T, typename W>
+static int launch_add_rmsnorm(float* resid, const void* delta, const void* weight, void* out,
+                              const int* rows, int n_out, int width, float eps, cudaStream_t s) {
+    const bool aligned = width % 4 == 0 && ((uintptr_t)resid % 16 == 0) &&
+                         ((uintptr_t)delta % 8 == 0) && ((uintptr_t)weight % 16 == 0) &&
+                         ((uintptr_t)out % 16 == 0);
+    const int quads = width / 4;
+#define VEC(CH, TH)                                                                           \
+    return de_launch(add_rmsnorm_vec_kernel<T, W, CH>, dim3(n_out), dim3(TH), 0, s, resid,    \
+                     (const T*)delta, (const W*)weight, (T*)out, rows, width, eps)
+    if (aligned && quads <= 128) VEC(1, 128);
+    if (aligned && quads <= 256) VEC(1, 256);
+    if (aligned && quads <= 512) VEC(2, 256);
+    if (aligned && quads <= 1024) VEC(4, 256);
+    if (aligned && quads <= 2048) VEC(4, 512);
+    if (aligned && quads <= 4096) VEC(8, 512);
+#undef VEC
+    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+    return de_launch(add_rmsnorm_kernel<T, W>, dim3(n_out), dim3(threads), 0, s, resid,
+                     (const T*)delta, (const W*)weight, (T*)out, rows, width, eps);
+}
+
 DE_EXPORT int de_add_rmsnorm(int dtype, int weight_dtype, float* resid, const void* delta,
                              const void* weight, void* out, const int* rows, int n_out, int width,
                              float eps, void* stream) {
     if (n_out <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
-    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
-#define LAUNCH(T, W)                                                                        \
-    add_rmsnorm_kernel<T, W><<<n_out, threads, 0, s>>>(resid, (const T*)delta, (const W*)weight, \
-                                                       (T*)out, rows, width, eps)
     if (dtype == DE_BF16) {
-        if (weight_dtype == DE_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
-        else LAUNCH(__nv_bfloat16, float);
-    } else {
-        if (weight_dtype == DE_BF16) LAUNCH(float, __nv_bfloat16);
-        else LAUNCH(float, float);
+        if (weight_dtype == DE_BF16)
+            return launch_add_rmsnorm<__nv_bfloat16, __nv_bfloat16>(resid, delta, weight, out, rows,
+                                                                    n_out, width, eps, s);
+        return launch_add_rmsnorm<__nv_bfloat16, float>(resid, delta, weight, out, rows, n_out,
+                                                        width, eps, s);
     }
-#undef LAUNCH
-    return de_check(cudaGetLastError());
+    if (weight_dtype == DE_BF16)
+        return launch_add_rmsnorm<float, __nv_bfloat16>(resid, delta, weight, out, rows, n_out,
+                                                        width, eps, s);
+    return launch_add_rmsnorm<float, float>(resid, delta, weight, out, rows, n_out, width, eps, s);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -130,6 +240,8 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride,
         kv_base = ((size_t)page_id * kv_heads) * page * d + (size_t)(pos % page) * d;
     }
     const size_t head_step = (size_t)page * d;          // from one kv head's slab to the next
+    pdl_wait();
+    pdl_trigger();
 
     // rotated pairs: threadIdx.x walks the pair index, threadIdx.y the heads
     for (int j = threadIdx.x; j < half; j += blockDim.x) {
@@ -179,14 +291,12 @@ DE_EXPORT int de_rope_kv_write(int dtype, void* qkv, int row_stride, const int* 
     int ty = 256 / tx;
     dim3 block(tx, ty);
 #define LAUNCH(T)                                                                              \
-    rope_kv_write_kernel<T><<<n, block, 0, s>>>((T*)qkv, row_stride, positions, token_slot,    \
-                                                inv_freq, rot, heads, kv_heads, d, (T*)k_pages, \
-                                                (T*)v_pages, block_table, table_stride, page,  \
-                                                write_kv, num_pages, status)
+    return de_launch(rope_kv_write_kernel<T>, dim3(n), block, 0, s, (T*)qkv, row_stride,       \
+                     positions, token_slot, inv_freq, rot, heads, kv_heads, d, (T*)k_pages,    \
+                     (T*)v_pages, block_table, table_stride, page, write_kv, num_pages, status)
     if (dtype == DE_BF16) LAUNCH(__nv_bfloat16);
-    else LAUNCH(float);
+    LAUNCH(float);
 #undef LAUNCH
-    return de_check(cudaGetLastError());
 }
 
 // ------------------------------------------------------------------------------------------
@@ -196,6 +306,8 @@ DE_EXPORT int de_rope_kv_write(int dtype, void* qkv, int row_stride, const int* 
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ x, T* __restrict__ out, int inner,
                                 size_t total) {
+    pdl_wait();
+    pdl_trigger();
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x) {
         const size_t n = idx / inner;
@@ -207,20 +319,47 @@ __global__ void silu_mul_kernel(const T* __restrict__ x, T* __restrict__ out, in
     }
 }
 
+// inner a multiple of 4: four outputs a thread, 8- or 16-byte accesses
+template <typename T>
+__global__ void silu_mul_vec_kernel(const T* __restrict__ x, T* __restrict__ out, int inner,
+                                    size_t total_quads) {
+    pdl_wait();
+    pdl_trigger();
+    const int quads = inner >> 2;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total_quads;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t n = idx / quads;
+        const int i = 4 * (int)(idx - n * quads);
+        float g[4], u[4], y[4];
+        Vec4<T>::load(x + n * 2 * inner + i, g);
+        Vec4<T>::load(x + n * 2 * inner + inner + i, u);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) y[e] = g[e] / (1.0f + expf(-g[e])) * u[e];
+        Vec4<T>::store(out + n * inner + i, y);
+    }
+}
+
 DE_EXPORT int de_silu_mul(int dtype, const void* x, void* out, int n, int inner, void* stream) {
     if (n <= 0) return 0;
-    const size_t total = (size_t)n * inner;
-    const int threads = 256;
-    size_t blocks = (total + threads - 1) / threads;
-    if (blocks > 148 * 16) blocks = 148 * 16;
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == DE_BF16)
-        silu_mul_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, s>>>(
-            (const __nv_bfloat16*)x, (__nv_bfloat16*)out, inner, total);
-    else
-        silu_mul_kernel<float><<<(int)blocks, threads, 0, s>>>((const float*)x, (float*)out, inner,
-                                                              total);
-    return de_check(cudaGetLastError());
+    const int threads = 256;
+    const bool vec = inner % 4 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)out % 16 == 0);
+    const size_t total = vec ? (size_t)n * (inner / 4) : (size_t)n * inner;
+    size_t blocks = (total + threads - 1) / threads;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    if (dtype == DE_BF16) {
+        if (vec)
+            return de_launch(silu_mul_vec_kernel<__nv_bfloat16>, dim3((unsigned)blocks),
+                             dim3(threads), 0, s, (const __nv_bfloat16*)x, (__nv_bfloat16*)out,
+                             inner, total);
+        return de_launch(silu_mul_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(threads), 0,
+                         s, (const __nv_bfloat16*)x, (__nv_bfloat16*)out, inner, total);
+    }
+    if (vec)
+        return de_launch(silu_mul_vec_kernel<float>, dim3((unsigned)blocks), dim3(threads), 0, s,
+                         (const float*)x, (float*)out, inner, total);
+    return de_launch(silu_mul_kernel<float>, dim3((unsigned)blocks), dim3(threads), 0, s,
+                     (const float*)x, (float*)out, inner, total);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -245,6 +384,8 @@ __global__ void sample_rows_kernel(const float* __restrict__ logits, int vocab,
                                    const int* __restrict__ position, int* __restrict__ out) {
     __shared__ float best_v[32];
     __shared__ int best_i[32];
+    pdl_wait();
+    pdl_trigger();
     const int r = blockIdx.x;
     const float* row = logits + (size_t)r * vocab;
     const float t = temperature ? temperature[r] : 0.0f;
@@ -290,7 +431,6 @@ __global__ void sample_rows_kernel(const float* __restrict__ logits, int vocab,
 DE_EXPORT int de_sample_rows(const float* logits, int rows, int vocab, const float* temperature,
                              const long long* seed, const int* position, int* out, void* stream) {
     if (rows <= 0) return 0;
-    sample_rows_kernel<<<rows, 1024, 0, (cudaStream_t)stream>>>(logits, vocab, temperature, seed,
-                                                                position, out);
-    return de_check(cudaGetLastError());
+    return de_launch(sample_rows_kernel, dim3(rows), dim3(1024), 0, (cudaStream_t)stream, logits,
+                     vocab, temperature, seed, position, out);
 }

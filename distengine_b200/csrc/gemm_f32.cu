@@ -8,6 +8,8 @@
 
 #include "common.cuh"
 
+DE_DEFINE_PDL_SWITCH
+
 namespace {
 
 constexpr int BM = 64;   // rows of x per block
@@ -34,6 +36,7 @@ gemm_f32_kernel(const float* __restrict__ x, const float* __restrict__ w, float*
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
 
+    pdl_wait();
     for (int k0 = 0; k0 < k_dim; k0 += BK) {
         float xv[4] = {0.f, 0.f, 0.f, 0.f}, wv[4] = {0.f, 0.f, 0.f, 0.f};
         const int gr = row0 + l_row, gc = col0 + l_row, gk = k0 + l_k;
@@ -76,6 +79,7 @@ gemm_f32_kernel(const float* __restrict__ x, const float* __restrict__ w, float*
                 for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
         }
     }
+    pdl_trigger();
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const int r = row0 + ty * 4 + i;
@@ -100,8 +104,8 @@ DE_EXPORT int de_gemm_f32(const float* x, const float* w, float* out, int n_rows
     const bool vec = (ldx % 4 == 0) && (ldw % 4 == 0) && (((uintptr_t)x) % 16 == 0) &&
                      (((uintptr_t)w) % 16 == 0);
     if (vec)
-        gemm_f32_kernel<true><<<grid, 256, 0, s>>>(x, w, out, n_rows, m_cols, k_dim, ldx, ldw, ldo);
-    else
-        gemm_f32_kernel<false><<<grid, 256, 0, s>>>(x, w, out, n_rows, m_cols, k_dim, ldx, ldw, ldo);
-    return de_check(cudaGetLastError());
+        return de_launch(gemm_f32_kernel<true>, grid, dim3(256), 0, s, x, w, out, n_rows, m_cols,
+                         k_dim, ldx, ldw, ldo);
+    return de_launch(gemm_f32_kernel<false>, grid, dim3(256), 0, s, x, w, out, n_rows, m_cols,
+                     k_dim, ldx, ldw, ldo);
 }

@@ -1,0 +1,242 @@
+// Matrix products for a handful of tokens (decode steps): out[m, n] = sum_k x[m, k] * w[n, k],
+// bfloat16 operands, float32 accumulation, for up to 32 rows of x.  Such a product only streams the
+// weight matrix once, so the kernel is built around the loads: every thread reads its weight rows in
+// 16-byte pieces that a quad of lanes strings together into full 128-byte lines, many in flight per
+// thread, straight into tensor-core fragments (no shared-memory staging), and feeds mma.sync
+// m16n8k16 with the weights as the 16-row operand and the tokens as the 8-column operand.
+//
+// Contiguous loads as fragments: lane (g, t) of a warp holds, for a block of 64 k, two pieces of 8
+// consecutive elements, k0 + 8 t .. + 7 and k0 + 32 + 8 t .. + 7, of weight rows g and g + 8 and of
+// token row g; the four lanes of a quad read 64 contiguous bytes of a row with one instruction.
+// Each piece feeds two mma steps (elements 0..3 and 4..7); the k order inside a step is permuted
+// against the usual layout, identically for both operands, which a sum over k does not see.
+//
+// The weights are no kernel's output, so the first blocks of them are requested before the kernel
+// waits for the kernel before it in the stream (programmatic dependent launch): the weight stream
+// of one product starts while the previous kernel is still finishing.
+//
+// A block of 8 warps owns 16 (or 8) weight rows; its warps take the 64-wide k blocks in turn and
+// their partial sums are added through shared memory.  Optional epilogue: silu(gate) * up, when
+// the matrix stacks the gate rows over the up rows ([2 inner, k]); a block then owns 16 gate rows
+// and the 16 up rows that belong to them, and writes inner outputs
+// (src/layers/activation.py:6-9, src/models/llama.py:23-27).
+//
+// Stands where the reference calls F.linear (src/layers/linear.py:19-20) on [B, 1, H] inputs.
+
+#include "common.cuh"
+
+DE_DEFINE_PDL_SWITCH
+
+namespace {
+
+constexpr int WARPS = 8;
+constexpr int KB = 64;                       // k elements per block
+
+__device__ __forceinline__ uint4 load_stream(const void* p) {      // weights: read once
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint4 load_cached(const void* p) {      // tokens: shared by all blocks
+    return *reinterpret_cast<const uint4*>(p);
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1, unsigned a2,
+                                         unsigned a3, unsigned b0, unsigned b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ const unsigned* regs(const uint4& v) {
+    return reinterpret_cast<const unsigned*>(&v);
+}
+
+template <typename OutT> __device__ __forceinline__ OutT to_out(float v);
+template <> __device__ __forceinline__ float to_out<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 to_out<__nv_bfloat16>(float v) {
+    return __float2bfloat16_rn(v);
+}
+
+// NT: token tiles of 8 (rows of x <= 8 NT).  ROWS: weight rows per block (16 or 8).
+// GATED: silu(gate) * up epilogue.
+template <int NT, int ROWS, bool GATED, typename OutT>
+__global__ void __launch_bounds__(WARPS * 32)
+linear_small_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ w,
+                    int ldw, OutT* __restrict__ out, int ldo, int m_rows, int n_out, int k_dim) {
+    constexpr int SETS = GATED ? 2 : 1;              // weight row sets per block
+    constexpr bool UPPER = ROWS == 16;               // rows g + 8 of the tile are in use
+    __shared__ float red[WARPS][SETS][16][NT * 8 + 1];
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int n0 = blockIdx.x * ROWS;
+
+    // weight rows of this lane (clamped: rows past the end are computed and dropped)
+    const __nv_bfloat16* wrow[SETS][2];
+#pragma unroll
+    for (int s = 0; s < SETS; ++s)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            int r = n0 + g + 8 * h;
+            r = r < n_out ? r : n_out - 1;
+            wrow[s][h] = w + (size_t)(r + s * n_out) * ldw + 8 * t;
+        }
+    const __nv_bfloat16* xrow[NT];
+    bool xlive[NT];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+        const int m = j * 8 + g;
+        xlive[j] = m < m_rows;
+        xrow[j] = x + (size_t)(xlive[j] ? m : 0) * ldx + 8 * t;
+    }
+
+    float acc[SETS][NT][4];
+#pragma unroll
+    for (int s = 0; s < SETS; ++s)
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[s][j][e] = 0.0f;
+
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    const int blocks = (k_dim + KB - 1) / KB;
+    // U blocks of k are loaded before any of them is multiplied: enough 16-byte loads in flight
+    // per thread (8 to 16) to keep the memory system busy with two or three blocks per SM
+    constexpr int LOADS = SETS * (UPPER ? 2 : 1) * 2 + NT * 2;
+    constexpr int U = 16 / LOADS > 0 ? 16 / LOADS : 1;
+    uint4 wv[U][SETS][2][2], xv[U][NT][2];
+
+    auto load_weights = [&](int b0) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int k0 = (b0 + u * WARPS) * KB;
+            // a piece past the end of k reads as zero (k is a multiple of 8: pieces are whole)
+            const bool ok0 = k0 + 8 * t + 8 <= k_dim, ok1 = k0 + 32 + 8 * t + 8 <= k_dim;
+#pragma unroll
+            for (int s = 0; s < SETS; ++s)
+#pragma unroll
+                for (int h = 0; h < (UPPER ? 2 : 1); ++h) {
+                    wv[u][s][h][0] = ok0 ? load_stream(wrow[s][h] + k0) : zero;
+                    wv[u][s][h][1] = ok1 ? load_stream(wrow[s][h] + k0 + 32) : zero;
+                }
+        }
+    };
+
+    load_weights(warp);
+    pdl_wait();                                   // x is the previous kernel's output
+
+    for (int b0 = warp; b0 < blocks;) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int k0 = (b0 + u * WARPS) * KB;
+            const bool ok0 = k0 + 8 * t + 8 <= k_dim, ok1 = k0 + 32 + 8 * t + 8 <= k_dim;
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                xv[u][j][0] = (ok0 && xlive[j]) ? load_cached(xrow[j] + k0) : zero;
+                xv[u][j][1] = (ok1 && xlive[j]) ? load_cached(xrow[j] + k0 + 32) : zero;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int p = 0; p < 2; ++p)                 // piece
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {           // half of a piece: one mma step
+#pragma unroll
+                    for (int s = 0; s < SETS; ++s) {
+                        const unsigned a0 = regs(wv[u][s][0][p])[2 * q];
+                        const unsigned a2 = regs(wv[u][s][0][p])[2 * q + 1];
+                        const unsigned a1 = UPPER ? regs(wv[u][s][1][p])[2 * q] : 0u;
+                        const unsigned a3 = UPPER ? regs(wv[u][s][1][p])[2 * q + 1] : 0u;
+#pragma unroll
+                        for (int j = 0; j < NT; ++j)
+                            mma_bf16(acc[s][j], a0, a1, a2, a3, regs(xv[u][j][p])[2 * q],
+                                     regs(xv[u][j][p])[2 * q + 1]);
+                    }
+                }
+        b0 += WARPS * U;
+        if (b0 < blocks) load_weights(b0);
+    }
+
+    // add the warps' partial sums
+#pragma unroll
+    for (int s = 0; s < SETS; ++s)
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            red[warp][s][g][j * 8 + 2 * t] = acc[s][j][0];
+            red[warp][s][g][j * 8 + 2 * t + 1] = acc[s][j][1];
+            red[warp][s][g + 8][j * 8 + 2 * t] = acc[s][j][2];
+            red[warp][s][g + 8][j * 8 + 2 * t + 1] = acc[s][j][3];
+        }
+    __syncthreads();
+    pdl_trigger();
+    for (int e = threadIdx.x; e < ROWS * m_rows; e += WARPS * 32) {
+        const int m = e / ROWS, r = e - m * ROWS;
+        const int n = n0 + r;
+        if (n >= n_out) continue;
+        float v[SETS];
+#pragma unroll
+        for (int s = 0; s < SETS; ++s) {
+            float sum = 0.0f;
+#pragma unroll
+            for (int wi = 0; wi < WARPS; ++wi) sum += red[wi][s][r][m];
+            v[s] = sum;
+        }
+        float y = v[0];
+        if constexpr (GATED) {
+            // the product's outputs are rounded to bfloat16 before the activation, as a separate
+            // product and activation would do
+            const float gate = __bfloat162float(__float2bfloat16_rn(v[0]));
+            const float up = __bfloat162float(__float2bfloat16_rn(v[SETS - 1]));
+            y = gate / (1.0f + expf(-gate)) * up;
+        }
+        out[(size_t)m * ldo + n] = to_out<OutT>(y);
+    }
+}
+
+template <int NT, int ROWS, bool GATED, typename OutT>
+int launch(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int m_rows,
+           int n_out, int k_dim, cudaStream_t s) {
+    const int grid = (n_out + ROWS - 1) / ROWS;
+    return de_launch(linear_small_kernel<NT, ROWS, GATED, OutT>, dim3(grid), dim3(WARPS * 32), 0, s,
+                     (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, ldw, (OutT*)out, ldo,
+                     m_rows, n_out, k_dim);
+}
+
+template <bool GATED, typename OutT>
+int pick(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int m_rows,
+         int n_out, int k_dim, cudaStream_t s) {
+    // few weight rows: blocks of 8 rows, so that there are blocks for every SM
+    const bool small = n_out < 16 * 2 * 148;
+#define GO(NT)                                                                                  \
+    return small ? launch<NT, 8, GATED, OutT>(x, ldx, w, ldw, out, ldo, m_rows, n_out, k_dim, s) \
+                 : launch<NT, 16, GATED, OutT>(x, ldx, w, ldw, out, ldo, m_rows, n_out, k_dim, s)
+    if (m_rows <= 8) { GO(1); }
+    if (m_rows <= 16) { GO(2); }
+    GO(4);
+#undef GO
+}
+
+}  // namespace
+
+DE_EXPORT int de_linear_small_max_rows() { return 32; }
+
+// out_f32: 1 for float32 output, 0 for bfloat16.  gated: w is [2 * n_out, k], gate rows first.
+DE_EXPORT int de_linear_small(const void* x, int ldx, const void* w, int ldw, void* out, int ldo,
+                              int m_rows, int n_out, int k_dim, int out_f32, int gated,
+                              void* stream) {
+    if (m_rows <= 0 || n_out <= 0) return 0;
+    if (m_rows > 32 || k_dim <= 0) return -2;
+    // 16-byte pieces: k a multiple of 8, rows that start on 16-byte boundaries
+    if (k_dim % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15))
+        return -3;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (gated) {
+        if (out_f32) return -4;
+        return pick<true, __nv_bfloat16>(x, ldx, w, ldw, out, ldo, m_rows, n_out, k_dim, s);
+    }
+    if (out_f32) return pick<false, float>(x, ldx, w, ldw, out, ldo, m_rows, n_out, k_dim, s);
+    return pick<false, __nv_bfloat16>(x, ldx, w, ldw, out, ldo, m_rows, n_out, k_dim, s);
+}

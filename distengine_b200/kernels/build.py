@@ -32,6 +32,7 @@ MODULES: dict[str, tuple[str, tuple[str, ...]]] = {
     "core": ("core.cu", ()),
     "gemm_f32": ("gemm_f32.cu", ()),
     "attention_simt": ("attention_simt.cu", ()),
+    "linear_small": ("linear_small.cu", ()),
     "attention_mma": ("attention_mma.cu", ()),          # built per head size: HEAD_DIM=<d>
 }
 
@@ -77,6 +78,9 @@ def library_path(module: str, defines: tuple[str, ...] = ()) -> tuple[str, str, 
     if module not in MODULES:
         raise BuildError(f"unknown kernel module '{module}'")
     source, libs = MODULES[module]
+    # extra definitions for experiments, e.g. DISTENGINE_B200_DEFINES="PDL_TRIGGER_LATE"
+    defines = tuple(defines) + tuple(d for d in os.environ.get("DISTENGINE_B200_DEFINES",
+                                                               "").split() if d)
     tag = "".join("_" + d.replace("=", "").replace("-D", "") for d in defines)
     name = f"{module}{tag}-{_digest(source, defines, libs)}.so"
     path = os.path.join(_build_dir(), name)

@@ -7,6 +7,7 @@ first kernel call raises ``KernelsUnavailable`` with the reason.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_void_p
 
 from . import build as _build
@@ -35,6 +36,10 @@ SIGNATURES: dict[str, dict[str, list]] = {
         "de_attn_simt_rows_per_tile": [],
         "de_attn_simt": [I, P, I, P, I, P, P, P, I, I, P, P, P, P, P, I, P, P, I, I, I, I, F, I, P],
         "de_attn_combine": [I, P, I, P, P, P, I, P, P, I, I, I, I, P],
+    },
+    "linear_small": {
+        "de_linear_small_max_rows": [],
+        "de_linear_small": [P, I, P, I, P, I, I, I, I, I, I, P],
     },
     "attention_mma": {
         "de_attn_mma_head_dim": [],
@@ -68,6 +73,11 @@ def load(module: str, defines: tuple[str, ...] = ()) -> ctypes.CDLL:
         fn = getattr(lib, name)
         fn.argtypes = argtypes
         fn.restype = c_int
+    # programmatic dependent launch (a kernel may start while the one before it finishes) is on
+    # unless DISTENGINE_B200_PDL=0
+    lib.de_set_pdl.argtypes = [c_int]
+    lib.de_set_pdl.restype = c_int
+    lib.de_set_pdl(0 if os.environ.get("DISTENGINE_B200_PDL", "1") == "0" else 1)
     _loaded[key] = lib
     return lib
 

@@ -153,12 +153,24 @@ def gemm_f32(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
            "gemm_f32")
 
 
+SMALL_ROWS = 32          # up to this many tokens a product streams the weights through linear_small
+
+
+def _small_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return (0 < x.shape[0] <= SMALL_ROWS and x.shape[1] % 8 == 0 and x.stride(1) == 1
+            and w.is_contiguous() and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+            and w.data_ptr() % 16 == 0)
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, out: "torch.Tensor | None" = None,
            out_dtype: "torch.dtype | None" = None) -> torch.Tensor:
-    """x @ w^T.  float32: this package's own kernel (true 32-bit).  bfloat16: the library matrix
-    product (cuBLAS through torch), where the reference calls a library too
-    (src/layers/linear.py:19-20); float32 accumulation, output bfloat16 or float32."""
-    out_dtype = out_dtype or x.dtype
+    """x @ w^T, float32 accumulation.
+
+    float32: this package's own CUDA-core kernel (true 32-bit).  bfloat16 with up to 32 rows
+    (decode steps): this package's weight-streaming kernel (``csrc/linear_small.cu``).  bfloat16
+    with more rows: the library matrix product (cuBLAS through torch), where the reference calls a
+    library too (src/layers/linear.py:19-20).  The output is bfloat16 or float32."""
+    out_dtype = out_dtype or (out.dtype if out is not None else x.dtype)
     if out is None:
         out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=x.device)
     if x.shape[0] == 0:
@@ -169,10 +181,40 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: "torch.Tensor | None" = None,
         return out
     _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16,
           "linear: operands must both be bfloat16 or both float32")
-    if out.dtype == torch.bfloat16:
+    _need(x.shape[1] == w.shape[1] and tuple(out.shape) == (x.shape[0], w.shape[0])
+          and out.stride(1) == 1, "linear: shapes do not agree")
+    if _small_ok(x, w):
+        lib = library.load("linear_small")
+        _check(lib.de_linear_small(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0),
+                                   out.data_ptr(), out.stride(0), x.shape[0], w.shape[0],
+                                   x.shape[1], int(out.dtype == torch.float32), 0, _stream()),
+               "linear_small")
+    elif out.dtype == torch.bfloat16:
         torch.mm(x, w.t(), out=out)
     else:
         torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
+    return out
+
+
+def linear_gated(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor,
+                 scratch: "torch.Tensor | None" = None) -> torch.Tensor:
+    """out[n, i] = silu(x . gate_i) * (x . up_i) for w_gate_up = [gate rows; up rows] of shape
+    [2 inner, k].  Up to 32 rows: one kernel (the product's epilogue applies the activation).
+    More rows: the product into ``scratch`` [N, 2 inner], then ``silu_mul``."""
+    inner = w_gate_up.shape[0] // 2
+    _need(tuple(out.shape) == (x.shape[0], inner), "linear_gated: out must be [N, inner]")
+    if x.shape[0] == 0:
+        return out
+    if x.dtype == torch.bfloat16 and _small_ok(x, w_gate_up) and out.stride(1) == 1:
+        lib = library.load("linear_small")
+        _check(lib.de_linear_small(x.data_ptr(), x.stride(0), w_gate_up.data_ptr(),
+                                   w_gate_up.stride(0), out.data_ptr(), out.stride(0), x.shape[0],
+                                   inner, x.shape[1], 0, 1, _stream()), "linear_small (gated)")
+        return out
+    if scratch is None:
+        scratch = torch.empty((x.shape[0], 2 * inner), dtype=x.dtype, device=x.device)
+    linear(x, w_gate_up, out=scratch)
+    silu_mul(scratch, out)
     return out
 
 

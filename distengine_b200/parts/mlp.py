@@ -34,10 +34,11 @@ class GatedMLP(FeedForward):
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         n = x.shape[0]
-        gate_up = ctx.buffer("mlp.gate_up", (n, 2 * self.inner))
-        ops.linear(x, self.w_gate_up, out=gate_up)
         act = ctx.buffer("mlp.act", (n, self.inner))
-        ops.silu_mul(gate_up, act)
+        scratch = None
+        if n > ops.SMALL_ROWS or self.dtype != torch.bfloat16:
+            scratch = ctx.buffer("mlp.gate_up", (n, 2 * self.inner))
+        ops.linear_gated(x, self.w_gate_up, act, scratch)
         out = ctx.buffer("mlp.out", (n, self.width))
         ops.linear(act, self.w_down, out=out)
         return out

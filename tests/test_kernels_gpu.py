@@ -331,3 +331,41 @@ def test_attention_refuses_sizes_it_does_not_take():
         AttentionLauncher(torch.float32, 4, 2, 33, 1.0, None)
     with pytest.raises(ValueError, match="multiple"):
         AttentionLauncher(torch.float32, 5, 2, 32, 1.0, None)
+
+
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 31, 32])
+@pytest.mark.parametrize("k,n", [(64, 50), (2048, 2560), (120, 331), (5632, 2048), (200, 8)])
+def test_linear_small(m, k, n):
+    """The weight-streaming product for a handful of tokens, plain and with float32 output."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(m * k + n)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(n, k, generator=g) * 0.1).to(torch.bfloat16)
+    from distengine_b200.kernels import ops as raw
+    assert raw._small_ok(x.to(DEV), w.to(DEV))
+    got = ops.linear(x.to(DEV), w.to(DEV))
+    assert_close(got, plain.plain_linear(x.float(), w.float(), torch.bfloat16), torch.bfloat16,
+                 "linear_small")
+    wide = ops.linear(x.to(DEV), w.to(DEV), out_dtype=torch.float32)
+    assert_close(wide, plain.plain_linear(x.float(), w.float(), torch.bfloat16, keep_f32=True),
+                 torch.float32, "linear_small -> f32")
+    # rows of a wider buffer as input (a row stride that is not the width)
+    buf = torch.zeros(m, k + 64, dtype=torch.bfloat16, device=DEV)
+    buf[:, :k] = x.to(DEV)
+    again = ops.linear(buf[:, :k], w.to(DEV))
+    assert torch.equal(again, got)
+
+
+@pytest.mark.parametrize("m", [1, 8, 13, 32, 40])
+@pytest.mark.parametrize("k,inner", [(64, 176), (2048, 5632), (120, 200)])
+def test_linear_gated(m, k, inner):
+    """silu(gate) * up in the product's epilogue (up to 32 rows) and as product + kernel."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(m + k + inner)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(2 * inner, k, generator=g) * 0.1).to(torch.bfloat16)
+    out = torch.empty(m, inner, dtype=torch.bfloat16, device=DEV)
+    ops.linear_gated(x.to(DEV), w.to(DEV), out)
+    gate = plain.plain_linear(x.float(), w[:inner].float(), torch.bfloat16)
+    up = plain.plain_linear(x.float(), w[inner:].float(), torch.bfloat16)
+    assert_close(out, plain.plain_swiglu(gate, up, torch.bfloat16), torch.bfloat16, "linear_gated")
