@@ -272,3 +272,89 @@ DE_EXPORT int de_attn_combine(int dtype, void* out, int out_stride, const int* s
                      out_stride, seq_qstart, seq_qlen, (const CombineItem*)items, partial_acc,
                      partial_ml, heads, kv_heads, d, rows_per_tile);
 }
+
+// ------------------------------------------------------------------------------------------
+// The variant that allocates nothing: see attention_static_scratch.h for who needs it and the
+// rules.  The scratch for the partial results is this file-scope device array.  Its name is a
+// device symbol: host code must not pass it to a kernel as if it were a pointer (on the host the
+// name stands for a shadow object, not for device memory); the device address is looked up once
+// per device with cudaGetSymbolAddress and that pointer is what the kernels get.
+// ------------------------------------------------------------------------------------------
+#include <cstdio>
+#include <mutex>
+
+#include "attention_static_scratch.h"
+
+static __device__ __align__(256) float g_static_scratch[DE_ATTN_STATIC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+float* g_scratch_address[MAX_DEVICES] = {};       // per device, filled at the first call there
+std::mutex g_scratch_mutex;
+thread_local char g_static_error[256] = "";
+
+// The device address of the array on the current device; looked up at the first call on it.
+int static_scratch_address(float** address) {
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return (int)e;
+    if (device < 0 || device >= MAX_DEVICES) return -11;
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    if (g_scratch_address[device] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess) return (int)e;
+        g_scratch_address[device] = static_cast<float*>(p);
+    }
+    *address = g_scratch_address[device];
+    return 0;
+}
+}  // namespace
+
+DE_EXPORT const char* de_attn_static_scratch_error(void) { return g_static_error; }
+
+DE_EXPORT int de_attn_simt_static_scratch(
+    int dtype, const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+    const void* v_pages, const int* block_table, int table_stride, int num_pages,
+    const int* seq_slot, const int* seq_qstart, const int* seq_qlen, const int* seq_pos0,
+    const int* items, int num_items, const int* combine_items, int num_combine, int num_partials,
+    int heads, int kv_heads, int head_dim, int page, float scale, int window, void* stream) {
+    g_static_error[0] = '\0';
+    if (num_items <= 0) return 0;
+    if (head_dim <= 0 || head_dim > MAX_D || kv_heads <= 0 || heads % kv_heads != 0 ||
+        num_partials < 0) {
+        std::snprintf(g_static_error, sizeof(g_static_error),
+                      "de_attn_simt_static_scratch: head_dim %d (1..%d), heads %d, kv_heads %d or "
+                      "num_partials %d cannot be used", head_dim, MAX_D, heads, kv_heads,
+                      num_partials);
+        return -2;
+    }
+    const long long rows = (long long)num_partials * kv_heads * ROWS;
+    const long long need = rows * (head_dim + 2);
+    if (need > DE_ATTN_STATIC_SCRATCH_FLOATS) {
+        std::snprintf(g_static_error, sizeof(g_static_error),
+                      "de_attn_simt_static_scratch: %d partial results x %d kv heads x %d rows x "
+                      "(head_dim %d + 2) = %lld floats, the built-in scratch array holds %d; use "
+                      "de_attn_simt with scratch of your own, or fewer chunks",
+                      num_partials, kv_heads, ROWS, head_dim, need, DE_ATTN_STATIC_SCRATCH_FLOATS);
+        return DE_ATTN_STATIC_TOO_LARGE;
+    }
+    float* scratch = nullptr;
+    const int status = static_scratch_address(&scratch);
+    if (status != 0) {
+        std::snprintf(g_static_error, sizeof(g_static_error),
+                      "de_attn_simt_static_scratch: the scratch array's device address could not "
+                      "be looked up (code %d)", status);
+        return status;
+    }
+    float* partial_acc = scratch;                               // [rows][head_dim]
+    float* partial_ml = scratch + rows * head_dim;              // [rows][2]
+    int code = de_attn_simt(dtype, q, q_stride, out, out_stride, k_pages, v_pages, block_table,
+                            table_stride, num_pages, seq_slot, seq_qstart, seq_qlen, seq_pos0,
+                            items, num_items, partial_acc, partial_ml, heads, kv_heads, head_dim,
+                            page, scale, window, stream);
+    if (code != 0) return code;
+    return de_attn_combine(dtype, out, out_stride, seq_qstart, seq_qlen, combine_items,
+                           num_combine, partial_acc, partial_ml, heads, kv_heads, head_dim, ROWS,
+                           stream);
+}
