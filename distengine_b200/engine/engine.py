@@ -52,7 +52,8 @@ class Engine:
         self.cache = CacheManager(specs, [e.reads_cache_of for e in self.model.plan],
                                   cfg.block_size, num_blocks, cfg.decode_batch_size, max_len,
                                   cfg.dtype, device)
-        self.runner = StepRunner(self.model, self.cache, use_graphs=cfg.use_graphs)
+        self.runner = StepRunner(self.model, self.cache, use_graphs=cfg.use_graphs,
+                                 use_fused=cfg.use_fused)
         self.scheduler = Scheduler(self.cache, cfg.max_batch_tokens, cfg.decode_batch_size,
                                    max_len, self.model.config.vocabulary)
         self.sampler = Sampler(device, cfg.decode_batch_size)

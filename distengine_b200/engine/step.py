@@ -43,7 +43,8 @@ def _align(n: int) -> int:
 
 
 class StepRunner:
-    def __init__(self, model, cache: CacheManager, use_graphs: bool = False) -> None:
+    def __init__(self, model, cache: CacheManager, use_graphs: bool = False,
+                 use_fused: bool = False) -> None:
         self.model, self.cache = model, cache
         self.device, self.dtype = model.device, model.dtype
         ops.require_device(self.device)
@@ -62,6 +63,12 @@ class StepRunner:
         self._graphs: dict[tuple, tuple] = {}
         self._meta_generation = 0
         self.graph_replays = 0
+        # the whole decode step as one persistent kernel, where the model has the shape for it
+        self.fused = None
+        if use_fused and hasattr(model, "blocks"):
+            from ..models.fused_decode import FusedDecoder
+            self.fused = FusedDecoder.try_build(model, cache)
+        self.fused_steps = 0
 
     # ------------------------------------------------------------------ host side
     def _validate(self, entries: list[StepEntry]) -> None:
@@ -163,19 +170,24 @@ class StepRunner:
             raise
         host = self._host_arrays(entries)
         graph_shape = None
-        if (self.use_graphs and int(host.seq_qlen.max()) == 1
+        fused = self.fused is not None and self.fused.takes(host)
+        if (self.use_graphs and not fused and int(host.seq_qlen.max()) == 1
                 and getattr(self.model, "graph_safe", True)):
             # a pure decode step: shape its arrays by the batch's shape only, so that it can be
             # replayed; the key range is capped at the next multiple of 512 positions
             longest = int(host.seq_pos0.max()) + 1
             graph_shape = {"context_cap": (longest + 511) // 512 * 512}
         prep = StepPrep(host, graph_shape)
-        self.model.prepare(prep)
+        if not fused:
+            self.model.prepare(prep)
         for name, array in (extra or {}).items():
             prep.add(name, array)
         ctx = self._upload(host, prep)
         self.last_arrays = ctx.arrays
-        if graph_shape is None:
+        if fused:
+            logits = self.fused.run(ctx)
+            self.fused_steps += 1
+        elif graph_shape is None:
             logits = self.model.forward(ctx, self.bindings)
         else:
             logits = self._forward_graphed(ctx, prep, graph_shape)

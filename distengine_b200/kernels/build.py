@@ -34,6 +34,7 @@ MODULES: dict[str, tuple[str, tuple[str, ...]]] = {
     "attention_simt": ("attention_simt.cu", ()),
     "linear_small": ("linear_small.cu", ()),
     "attention_mma": ("attention_mma.cu", ()),          # built per head size: HEAD_DIM=<d>
+    "decode_fused": ("decode_fused.cu", ()),            # built per head size: HEAD_DIM=<d>
 }
 
 

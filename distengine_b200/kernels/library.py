@@ -41,6 +41,11 @@ SIGNATURES: dict[str, dict[str, list]] = {
         "de_linear_small_max_rows": [],
         "de_linear_small": [P, I, P, I, P, I, I, I, I, I, I, P],
     },
+    "decode_fused": {
+        "de_decode_fused_head_dim": [], "de_decode_fused_max_tokens": [],
+        "de_decode_fused_args_bytes": [], "de_decode_fused_layer_bytes": [],
+        "de_decode_fused_grid": [I], "de_decode_fused": [P, I, P],
+    },
     "attention_mma": {
         "de_attn_mma_head_dim": [],
         "de_attn_mma": [I, P, I, P, I, P, P, P, I, I, P, P, P, P, P, I, P, P, I, I, I, I, F, I, P],
@@ -53,8 +58,9 @@ _loaded: dict[tuple[str, tuple[str, ...]], ctypes.CDLL] = {}
 def default_build_requests() -> list[tuple[str, tuple[str, ...]]]:
     """Every module; the per-head-size attention for the head sizes of common models."""
     requests = [(module, ()) for module in _build.MODULES
-                if module in SIGNATURES and module != "attention_mma"]
-    return requests + [("attention_mma", (f"HEAD_DIM={d}",)) for d in (64, 128)]
+                if module in SIGNATURES and module not in ("attention_mma", "decode_fused")]
+    return (requests + [("attention_mma", (f"HEAD_DIM={d}",)) for d in (64, 128)]
+            + [("decode_fused", (f"HEAD_DIM={d}",)) for d in (64, 128)])
 
 
 def load(module: str, defines: tuple[str, ...] = ()) -> ctypes.CDLL:

@@ -109,3 +109,28 @@ def test_cuts_agree_with_each_other(dtype_name, model_root):
     for schedule, rows in results.items():
         for key, got in rows.items():
             assert_close(got, base[key], DTYPES[dtype_name], f"{schedule} against whole {key}")
+
+
+@pytest.mark.parametrize("name", ["tiny_b", "tiny_d"])
+def test_persistent_decode_kernel_matches_plain(name, model_root):
+    """The optional single-kernel decode step (csrc/decode_fused.cu): steps of single tokens go
+    through it, everything else through the kernels of the parts; same logits."""
+    from distengine_b200.engine.replay import build_runner
+    folder, config, requests, reference = _model(name, model_root)
+    dtype = torch.bfloat16
+    used = 0
+    for schedule in ("tail", "mixed"):
+        steps, max_tokens = _schedules(requests)[schedule]
+        runner = build_runner(folder, "bfloat16", max_tokens,
+                              page_size=tiny_configs.ALL[name]["page_size"],
+                              poison_freed_pages=True, use_fused=True)
+        assert runner.fused is not None
+        with tempfile.TemporaryDirectory() as out:
+            th.replay_in_process(runner, steps, out)
+            rows = th.collect(steps, out, config["vocab_size"])
+        used += runner.fused_steps
+        for rid in requests:
+            positions = sorted(p for r, p in rows if r == rid)
+            got = np.stack([rows[(rid, p)] for p in positions])
+            assert_close(got, reference[dtype][rid][positions], dtype, f"{name} fused {schedule} {rid}")
+    assert used > 50

@@ -34,7 +34,17 @@ TINY_C = dict(
     prompts=(3, 50), max_new_tokens=6, temperature=0.0,
 )
 
-ALL = {"tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C}
+# a shape the persistent decode kernel takes (head size a multiple of 32), grouped-query
+TINY_D = dict(
+    config=dict(architectures=["LlamaForCausalLM"], vocab_size=300, hidden_size=192,
+                intermediate_size=328, num_hidden_layers=2, num_attention_heads=6,
+                num_key_value_heads=2, head_dim=64, rms_norm_eps=2e-5, rope_theta=50000.0,
+                max_position_embeddings=256, tie_word_embeddings=False),
+    seed=3, norm_init="uniform", page_size=16,
+    prompts=(4, 30), max_new_tokens=6, temperature=0.0,
+)
+
+ALL = {"tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C, "tiny_d": TINY_D}
 
 
 def make_folder(name: str, root: str, dtype: str = "float32") -> str:
