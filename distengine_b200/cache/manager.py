@@ -241,6 +241,11 @@ class CacheManager:
     def _missing(self, group: _PagedGroup, request_id: str, old_len: int,
                  new_len: int) -> list[int]:
         table = group.tables[request_id]
+        if new_len <= len(table) * self.page_size and (old_len // self.page_size
+                                                       == (new_len - 1) // self.page_size):
+            # the new positions lie in the page that holds the last position: it is held
+            if table and table[(new_len - 1) // self.page_size] >= 0:
+                return []
         first = self._first_needed(group, old_len)
         last = (new_len + self.page_size - 1) // self.page_size
         return [p for p in range(first, last) if p >= len(table) or table[p] < 0]

@@ -49,6 +49,16 @@ class Request:
     def token_ids(self) -> list[int]:
         return self.prompt_token_ids + self.generated_token_ids
 
+    def tokens_from(self, start: int, count: int) -> list[int]:
+        """``token_ids[start: start + count]`` without joining the two lists."""
+        p = len(self.prompt_token_ids)
+        end = start + count
+        if end <= p:
+            return self.prompt_token_ids[start:end]
+        if start >= p:
+            return self.generated_token_ids[start - p: end - p]
+        return self.prompt_token_ids[start:] + self.generated_token_ids[: end - p]
+
     @property
     def num_tokens(self) -> int:
         return len(self.prompt_token_ids) + len(self.generated_token_ids)

@@ -127,7 +127,8 @@ class Scheduler:
                     break
                 free -= need
                 budget -= 1
-                plan.entries.append(PlannedEntry(request, [request.token_ids[-1]], True))
+                plan.entries.append(PlannedEntry(request, request.tokens_from(request.num_tokens - 1, 1),
+                                                 True))
             if victim is not None:
                 self._preempt(victim, plan)
                 continue
@@ -141,7 +142,7 @@ class Scheduler:
                     continue
                 free -= self._pages_for(request, count)
                 budget -= count
-                tokens = request.token_ids[request.num_computed: request.num_computed + count]
+                tokens = request.tokens_from(request.num_computed, count)
                 plan.entries.append(PlannedEntry(request, tokens, count == left))
             # 3. admissions
             while (self.waiting and budget > 0 and len(self.running) < self.max_seqs
@@ -156,7 +157,7 @@ class Scheduler:
                 self.running.append(request)
                 free -= self._pages_for(request, count)
                 budget -= count
-                tokens = request.token_ids[: count]
+                tokens = request.tokens_from(0, count)
                 plan.entries.append(PlannedEntry(request, tokens, count == left))
             if plan.entries or not self.running:
                 if not plan.entries and self.waiting:

@@ -62,6 +62,7 @@ class StepRunner:
         # decode steps replayed as CUDA graphs: key -> (graph, logits, kernels in it, generation)
         self._graphs: dict[tuple, tuple] = {}
         self._meta_generation = 0
+        self._layouts: dict[tuple, tuple] = {}
         self.graph_replays = 0
         # the whole decode step as one persistent kernel, where the model has the shape for it
         self.fused = None
@@ -123,16 +124,25 @@ class StepRunner:
             self._host_meta = torch.empty(cap, dtype=torch.int32).pin_memory()
             self._dev_meta = torch.empty(cap, dtype=torch.int32, device=self.device)
             self._meta_generation += 1
+            self._layouts = {}
         self.upload_bytes = total * 4
         if self._upload_pending:
             self._uploaded.synchronize()          # the staging buffer is free again
         stage = self._host_meta.numpy()
-        views: dict[str, torch.Tensor] = {}
-        offset = 0
-        for name, array in arrays:
+        # where each array lies depends on the arrays' names and shapes only: keep the device
+        # views of a layout (steady decoding repeats one layout step after step)
+        layout_key = tuple((name, array.shape) for name, array in arrays)
+        layout = self._layouts.get(layout_key)
+        if layout is None:
+            views, offsets, offset = {}, [], 0
+            for name, array in arrays:
+                views[name] = self._dev_meta[offset: offset + array.size].view(array.shape)
+                offsets.append(offset)
+                offset += _align(array.size)
+            layout = self._layouts[layout_key] = (views, offsets)
+        views, offsets = layout
+        for (name, array), offset in zip(arrays, offsets):
             stage[offset: offset + array.size] = array.reshape(-1)
-            views[name] = self._dev_meta[offset: offset + array.size].view(array.shape)
-            offset += _align(array.size)
         self._dev_meta[:total].copy_(self._host_meta[:total], non_blocking=True)
         self.cache.flush_tables()
         self._uploaded.record()

@@ -97,6 +97,11 @@ class AttentionLauncher:
         total_tiles = sum(int(((q.astype(np.int64) * self.group + s.rows - 1) // s.rows).sum())
                           for q, s in zip(parts, self.shapes))
         for qlen, shape in zip(parts, self.shapes):
+            if not int(qlen.sum()):                      # no sequence takes this tile shape
+                prep.add(f"{self.key}/{shape.name}/items", np.zeros((0, 8), dtype=np.int32))
+                prep.add(f"{self.key}/{shape.name}/combine", np.zeros((0, 4), dtype=np.int32))
+                notes[shape.name] = 0
+                continue
             chunk = chunks_cap = None
             if force_chunk is not None:
                 chunk, chunks_cap = force_chunk, force_cap

@@ -103,9 +103,27 @@ class DecoderModel:
         return all(part.graph_safe for block in self.blocks for part in block.parts().values())
 
     def prepare(self, prep: StepPrep) -> None:
-        for block in self.blocks:
-            for part in block.parts().values():
-                part.prepare(prep)
+        for part in self._preparers():
+            part.prepare(prep)
+
+    def _preparers(self):
+        """The parts whose ``prepare`` does something, one for each distinct plan key (layers of
+        the same shape share their work lists); found once."""
+        cached = getattr(self, "_preparer_list", None)
+        if cached is None:
+            from ..parts.base import Part
+            cached, seen = [], set()
+            for block in self.blocks:
+                for part in block.parts().values():
+                    if type(part).prepare is Part.prepare:
+                        continue
+                    key = getattr(part, "prepare_key", None)
+                    if key is not None and key in seen:
+                        continue
+                    seen.add(key)
+                    cached.append(part)
+            self._preparer_list = cached
+        return cached
 
     def forward(self, ctx: StepContext,
                 caches: "list[CacheBinding | None]") -> torch.Tensor:

@@ -54,6 +54,11 @@ class PagedAttention(Mixer):
         return PagedKVSpec(self.kv_heads, self.head_dim, self.window)
 
     # ------------------------------------------------------------------ step
+    @property
+    def prepare_key(self) -> str:
+        """Layers with the same key share one plan of a step's attention work."""
+        return self.kernels.key
+
     def prepare(self, prep: StepPrep) -> None:
         self.kernels.prepare(prep)
 
