@@ -75,8 +75,11 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     return *reinterpret_cast<const unsigned*>(&v);
 }
 
-// WM warps along the rows (16 rows each), WN warps along the keys of a tile; WM * WN = 4.
-template <int WM, int WN>
+// WM warps along the rows, WN warps along the keys of a tile; WM * WN = 4.  Each warp owns RT
+// m16 row tiles (16 RT rows) that share every key/value fragment it reads from shared memory:
+// with RT = 2 a fragment feeds two mma instructions, which halves the shared-memory traffic per
+// flop (the wide shape is bound by it).
+template <int WM, int WN, int RT>
 __global__ void __launch_bounds__(THREADS)
 attn_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* __restrict__ out,
                 int out_stride, const __nv_bfloat16* __restrict__ k_pages,
@@ -86,11 +89,13 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16
                 const int* __restrict__ seq_pos0, const WorkItem* __restrict__ items,
                 float* __restrict__ partial_acc, float* __restrict__ partial_ml, int heads,
                 int kv_heads, int page, float scale, int window) {
-    constexpr int ROWS = WM * 16;          // rows of the tile
+    static_assert(WN == 1 || RT == 1, "warps that split the keys own one row tile");
+    constexpr int ROWS = WM * 16 * RT;     // rows of the tile
     constexpr int NK = KT / WN;            // keys of a tile that one warp sees
     constexpr int NT = NK / 8;             // score tiles (n = 8) per warp
     constexpr int DT = D / 8;              // output tiles (n = 8)
     constexpr int CHUNKS = D / 8;          // 16-byte copies in one key's row
+    constexpr int R2 = 2 * RT;             // rows of one thread
 
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);        // [2][KT][LDS]
@@ -110,32 +115,34 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16
     const int wm = warp / WN, wn = warp % WN;
     const int gid = lane >> 2, tig = lane & 3;
 
-    // the two rows of this thread: gid and gid + 8 of the warp's 16
-    int row[2], pos[2], tok[2], hq[2];
-    bool live[2];
+    // the rows of this thread: gid and gid + 8 of each of the warp's row tiles
+    int row[R2], pos[R2], tok[R2], hq[R2];
+    bool live[R2];
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        row[i] = it.row0 + wm * 16 + gid + 8 * i;
-        live[i] = row[i] < rows_total;
-        tok[i] = live[i] ? row[i] / g : 0;
-        hq[i] = hk * g + (live[i] ? row[i] % g : 0);
-        pos[i] = live[i] ? pos0 + tok[i] : -1;
+    for (int r = 0; r < R2; ++r) {
+        row[r] = it.row0 + (wm * RT + (r >> 1)) * 16 + gid + 8 * (r & 1);
+        live[r] = row[r] < rows_total;
+        tok[r] = live[r] ? row[r] / g : 0;
+        hq[r] = hk * g + (live[r] ? row[r] % g : 0);
+        pos[r] = live[r] ? pos0 + tok[r] : -1;
     }
 
     pdl_wait();            // q, and the keys and values of this step's tokens, are just written
 
     // q fragments straight from global memory (read once)
-    unsigned qf[D / 16][4];
+    unsigned qf[RT][D / 16][4];
 #pragma unroll
-    for (int kk = 0; kk < D / 16; ++kk) {
+    for (int rt = 0; rt < RT; ++rt)
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const __nv_bfloat16* p = q + (size_t)(tok0 + tok[i]) * q_stride + hq[i] * D + kk * 16 +
-                                     2 * tig;
-            qf[kk][i] = live[i] ? *reinterpret_cast<const unsigned*>(p) : 0u;
-            qf[kk][i + 2] = live[i] ? *reinterpret_cast<const unsigned*>(p + 8) : 0u;
-        }
-    }
+        for (int kk = 0; kk < D / 16; ++kk)
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int r = 2 * rt + i;
+                const __nv_bfloat16* p = q + (size_t)(tok0 + tok[r]) * q_stride + hq[r] * D +
+                                         kk * 16 + 2 * tig;
+                qf[rt][kk][i] = live[r] ? *reinterpret_cast<const unsigned*>(p) : 0u;
+                qf[rt][kk][i + 2] = live[r] ? *reinterpret_cast<const unsigned*>(p + 8) : 0u;
+            }
 
     // key range of the tile and of this thread's rows
     const int last_row = min(it.row0 + ROWS, rows_total) - 1;
@@ -144,15 +151,17 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16
     int k_lo_true = it.kv_begin;
     if (window > 0) k_lo_true = max(k_lo_true, min_pos - window + 1);
     const int k_lo = (k_lo_true / KT) * KT;
-    int lo[2], hi[2];
+    int lo[R2], hi[R2];
+    int min_hi = 0x7fffffff, max_lo = 0;
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        lo[i] = it.kv_begin;
-        if (window > 0) lo[i] = max(lo[i], pos[i] - window + 1);
-        hi[i] = min(it.kv_end, pos[i] + 1);          // pos -1 (dead row): nothing is visible
+    for (int r = 0; r < R2; ++r) {
+        lo[r] = it.kv_begin;
+        if (window > 0) lo[r] = max(lo[r], pos[r] - window + 1);
+        hi[r] = min(it.kv_end, pos[r] + 1);          // pos -1 (dead row): nothing is visible
+        min_hi = min(min_hi, hi[r]);
+        max_lo = max(max_lo, lo[r]);
     }
-    // over the warp: is every key of a tile visible to every row?  (rows gid differ per lane)
-    int min_hi = min(hi[0], hi[1]), max_lo = max(lo[0], lo[1]);
+    // over the warp: is every key of a tile visible to every row?  (rows differ per lane)
 #pragma unroll
     for (int o = 4; o < 32; o <<= 1) {
         min_hi = min(min_hi, __shfl_xor_sync(0xffffffffu, min_hi, o));
@@ -179,12 +188,16 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16
         }
     };
 
-    float o_acc[DT][4];
+    float o_acc[RT][DT][4];
 #pragma unroll
-    for (int j = 0; j < DT; ++j)
+    for (int rt = 0; rt < RT; ++rt)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) o_acc[j][e] = 0.0f;
-    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+        for (int j = 0; j < DT; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o_acc[rt][j][e] = 0.0f;
+    float m_run[R2], l_run[R2];
+#pragma unroll
+    for (int r = 0; r < R2; ++r) { m_run[r] = -INFINITY; l_run[r] = 0.0f; }
     const float sl = scale * 1.4426950408889634f;           // scores in the exp2 domain
 
     load_tile(k_lo, 0);
@@ -199,12 +212,14 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16
         const __nv_bfloat16* kb = k_s + stage * KT * LDS + wn * NK * LDS;
         const __nv_bfloat16* vb = v_s + stage * KT * LDS + wn * NK * LDS;
 
-        // s = q k^T : 16 rows x NK keys
-        float s[NT][4];
+        // s = q k^T : 16 RT rows x NK keys
+        float s[RT][NT][4];
 #pragma unroll
-        for (int j = 0; j < NT; ++j)
+        for (int rt = 0; rt < RT; ++rt)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) s[j][e] = 0.0f;
+            for (int j = 0; j < NT; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[rt][j][e] = 0.0f;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
 #pragma unroll
@@ -212,8 +227,11 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16
                 unsigned b[4];
                 const int mat = lane >> 3, r = lane & 7;
                 ldmatrix_x4(b, kb + ((j + (mat >> 1)) * 8 + r) * LDS + kk * 16 + (mat & 1) * 8);
-                mma_bf16(s[j], qf[kk], b[0], b[1]);
-                mma_bf16(s[j + 1], qf[kk], b[2], b[3]);
+#pragma unroll
+                for (int rt = 0; rt < RT; ++rt) {
+                    mma_bf16(s[rt][j], qf[rt][kk], b[0], b[1]);
+                    mma_bf16(s[rt][j + 1], qf[rt][kk], b[2], b[3]);
+                }
             }
         }
 
@@ -221,47 +239,55 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16
         const int key0 = kt + wn * NK;
         if (key0 + NK > min_hi || key0 < max_lo) {
 #pragma unroll
-            for (int j = 0; j < NT; ++j)
+            for (int rt = 0; rt < RT; ++rt)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int key = key0 + j * 8 + 2 * tig + (e & 1);
-                    const int i = e >> 1;
-                    if (key < lo[i] || key >= hi[i]) s[j][e] = -INFINITY;
-                }
+                for (int j = 0; j < NT; ++j)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int key = key0 + j * 8 + 2 * tig + (e & 1);
+                        const int r = 2 * rt + (e >> 1);
+                        if (key < lo[r] || key >= hi[r]) s[rt][j][e] = -INFINITY;
+                    }
         }
 
         // running softmax
-        float m_new[2] = {m_run[0], m_run[1]};
+        unsigned pf[RT][NK / 16][4];
 #pragma unroll
-        for (int j = 0; j < NT; ++j) {
-            m_new[0] = fmaxf(m_new[0], fmaxf(s[j][0], s[j][1]));
-            m_new[1] = fmaxf(m_new[1], fmaxf(s[j][2], s[j][3]));
-        }
-        float corr[2], m_use[2], l_add[2] = {0.0f, 0.0f};
+        for (int rt = 0; rt < RT; ++rt) {
+            float m_new[2] = {m_run[2 * rt], m_run[2 * rt + 1]};
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 1));
-            m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 2));
-            m_use[i] = m_new[i] == -INFINITY ? 0.0f : m_new[i];
-            corr[i] = fast_exp2((m_run[i] - m_use[i]) * sl);        // 0 while m_run is -inf
-            m_run[i] = m_new[i];
-        }
-        unsigned pf[NK / 16][4];
+            for (int j = 0; j < NT; ++j) {
+                m_new[0] = fmaxf(m_new[0], fmaxf(s[rt][j][0], s[rt][j][1]));
+                m_new[1] = fmaxf(m_new[1], fmaxf(s[rt][j][2], s[rt][j][3]));
+            }
+            float corr[2], m_use[2], l_add[2] = {0.0f, 0.0f};
 #pragma unroll
-        for (int j = 0; j < NT; ++j) {
-            const float p0 = fast_exp2((s[j][0] - m_use[0]) * sl), p1 = fast_exp2((s[j][1] - m_use[0]) * sl);
-            const float p2 = fast_exp2((s[j][2] - m_use[1]) * sl), p3 = fast_exp2((s[j][3] - m_use[1]) * sl);
-            l_add[0] += p0 + p1;
-            l_add[1] += p2 + p3;
-            pf[j >> 1][(j & 1) * 2] = pack_bf16(p0, p1);
-            pf[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
-        }
+            for (int i = 0; i < 2; ++i) {
+                m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 1));
+                m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 2));
+                m_use[i] = m_new[i] == -INFINITY ? 0.0f : m_new[i];
+                corr[i] = fast_exp2((m_run[2 * rt + i] - m_use[i]) * sl);   // 0 while m_run is -inf
+                m_run[2 * rt + i] = m_new[i];
+            }
 #pragma unroll
-        for (int i = 0; i < 2; ++i) l_run[i] = l_run[i] * corr[i] + l_add[i];
+            for (int j = 0; j < NT; ++j) {
+                const float p0 = fast_exp2((s[rt][j][0] - m_use[0]) * sl);
+                const float p1 = fast_exp2((s[rt][j][1] - m_use[0]) * sl);
+                const float p2 = fast_exp2((s[rt][j][2] - m_use[1]) * sl);
+                const float p3 = fast_exp2((s[rt][j][3] - m_use[1]) * sl);
+                l_add[0] += p0 + p1;
+                l_add[1] += p2 + p3;
+                pf[rt][j >> 1][(j & 1) * 2] = pack_bf16(p0, p1);
+                pf[rt][j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
+            }
 #pragma unroll
-        for (int j = 0; j < DT; ++j) {
-            o_acc[j][0] *= corr[0]; o_acc[j][1] *= corr[0];
-            o_acc[j][2] *= corr[1]; o_acc[j][3] *= corr[1];
+            for (int i = 0; i < 2; ++i)
+                l_run[2 * rt + i] = l_run[2 * rt + i] * corr[i] + l_add[i];
+#pragma unroll
+            for (int j = 0; j < DT; ++j) {
+                o_acc[rt][j][0] *= corr[0]; o_acc[rt][j][1] *= corr[0];
+                o_acc[rt][j][2] *= corr[1]; o_acc[rt][j][3] *= corr[1];
+            }
         }
 
         // o += p v
@@ -273,8 +299,11 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16
                 const int mat = lane >> 3, r = lane & 7;
                 ldmatrix_x4_trans(b, vb + (ks * 16 + (mat & 1) * 8 + r) * LDS +
                                          (jd + (mat >> 1)) * 8);
-                mma_bf16(o_acc[jd], pf[ks], b[0], b[1]);
-                mma_bf16(o_acc[jd + 1], pf[ks], b[2], b[3]);
+#pragma unroll
+                for (int rt = 0; rt < RT; ++rt) {
+                    mma_bf16(o_acc[rt][jd], pf[rt][ks], b[0], b[1]);
+                    mma_bf16(o_acc[rt][jd + 1], pf[rt][ks], b[2], b[3]);
+                }
             }
         }
         __syncthreads();                       // this stage may be overwritten by the next load
@@ -284,33 +313,34 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16
 
     // row sums live in the 4 lanes of a quad
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
-        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
+    for (int r = 0; r < R2; ++r) {
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
     }
 
     if constexpr (WN == 1) {
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            if (!live[i]) continue;
+        for (int r = 0; r < R2; ++r) {
+            if (!live[r]) continue;
+            const int rt = r >> 1, i = r & 1;
             if (it.partial < 0) {
-                const float inv = l_run[i] > 0.0f ? 1.0f / l_run[i] : 0.0f;
-                __nv_bfloat16* o = out + (size_t)(tok0 + tok[i]) * out_stride + hq[i] * D;
+                const float inv = l_run[r] > 0.0f ? 1.0f / l_run[r] : 0.0f;
+                __nv_bfloat16* o = out + (size_t)(tok0 + tok[r]) * out_stride + hq[r] * D;
 #pragma unroll
                 for (int j = 0; j < DT; ++j)
                     *reinterpret_cast<unsigned*>(o + j * 8 + 2 * tig) =
-                        pack_bf16(o_acc[j][2 * i] * inv, o_acc[j][2 * i + 1] * inv);
+                        pack_bf16(o_acc[rt][j][2 * i] * inv, o_acc[rt][j][2 * i + 1] * inv);
             } else {
-                const size_t idx = ((size_t)it.partial * kv_heads + hk) * ROWS + (row[i] - it.row0);
+                const size_t idx = ((size_t)it.partial * kv_heads + hk) * ROWS + (row[r] - it.row0);
                 float* pa = partial_acc + idx * D;
 #pragma unroll
                 for (int j = 0; j < DT; ++j) {
-                    pa[j * 8 + 2 * tig] = o_acc[j][2 * i];
-                    pa[j * 8 + 2 * tig + 1] = o_acc[j][2 * i + 1];
+                    pa[j * 8 + 2 * tig] = o_acc[rt][j][2 * i];
+                    pa[j * 8 + 2 * tig + 1] = o_acc[rt][j][2 * i + 1];
                 }
                 if (tig == 0) {
-                    partial_ml[idx * 2] = m_run[i] * scale;      // natural-log domain, as merged
-                    partial_ml[idx * 2 + 1] = l_run[i];
+                    partial_ml[idx * 2] = m_run[r] * scale;      // natural-log domain, as merged
+                    partial_ml[idx * 2 + 1] = l_run[r];
                 }
             }
         }
@@ -326,8 +356,8 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16
             float* dst = red_o + ((size_t)wn * 16 + r) * D;
 #pragma unroll
             for (int j = 0; j < DT; ++j) {
-                dst[j * 8 + 2 * tig] = o_acc[j][2 * i];
-                dst[j * 8 + 2 * tig + 1] = o_acc[j][2 * i + 1];
+                dst[j * 8 + 2 * tig] = o_acc[0][j][2 * i];
+                dst[j * 8 + 2 * tig + 1] = o_acc[0][j][2 * i + 1];
             }
             if (tig == 0) {
                 red_m[wn * 16 + r] = m_run[i];
@@ -367,7 +397,9 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16
     }
 }
 
-template <int WM, int WN>
+constexpr int WIDE_RT = D <= 64 ? 2 : 1;       // row tiles per warp of the wide shape
+
+template <int WM, int WN, int RT>
 int launch(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
            const void* v_pages, const int* block_table, int table_stride, int num_pages,
            const int* seq_slot, const int* seq_qstart, const int* seq_qlen, const int* seq_pos0,
@@ -376,7 +408,7 @@ int launch(const void* q, int q_stride, void* out, int out_stride, const void* k
     size_t smem = (size_t)4 * KT * LDS * sizeof(__nv_bfloat16);
     const size_t red = (size_t)WN * 16 * (D + 2) * sizeof(float);
     if (WN > 1 && red > smem) smem = red;
-    auto kernel = attn_mma_kernel<WM, WN>;
+    auto kernel = attn_mma_kernel<WM, WN, RT>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)smem);
@@ -394,7 +426,10 @@ int launch(const void* q, int q_stride, void* out, int out_stride, const void* k
 
 DE_EXPORT int de_attn_mma_head_dim() { return D; }
 
-// shape 0: wide (64 rows a tile), shape 1: narrow (16 rows a tile)
+// rows of a tile of each shape (the host plans with these)
+DE_EXPORT int de_attn_mma_rows(int shape) { return shape == 0 ? 4 * 16 * WIDE_RT : 16; }
+
+// shape 0: wide (64 or 128 rows a tile), shape 1: narrow (16 rows a tile)
 DE_EXPORT int de_attn_mma(int shape, const void* q, int q_stride, void* out, int out_stride,
                           const void* k_pages, const void* v_pages, const int* block_table,
                           int table_stride, int num_pages, const int* seq_slot,
@@ -407,11 +442,11 @@ DE_EXPORT int de_attn_mma(int shape, const void* q, int q_stride, void* out, int
     if (q_stride % 2 != 0 || out_stride % 2 != 0) return -3;
     cudaStream_t s = (cudaStream_t)stream;
     if (shape == 0)
-        return launch<4, 1>(q, q_stride, out, out_stride, k_pages, v_pages, block_table,
+        return launch<4, 1, WIDE_RT>(q, q_stride, out, out_stride, k_pages, v_pages, block_table,
                             table_stride, num_pages, seq_slot, seq_qstart, seq_qlen, seq_pos0, items,
                             num_items, partial_acc, partial_ml, heads, kv_heads, page, scale, window,
                             s);
-    return launch<1, 4>(q, q_stride, out, out_stride, k_pages, v_pages, block_table, table_stride,
+    return launch<1, 4, 1>(q, q_stride, out, out_stride, k_pages, v_pages, block_table, table_stride,
                         num_pages, seq_slot, seq_qstart, seq_qlen, seq_pos0, items, num_items,
                         partial_acc, partial_ml, heads, kv_heads, page, scale, window, s);
 }

@@ -58,6 +58,7 @@ class Engine:
                                    max_len, self.model.config.vocabulary)
         self.sampler = Sampler(device, cfg.decode_batch_size)
         self.completed: deque[dict] = deque()
+        self._ahead = None                      # the next step, prepared while this one runs
         self.requests: dict[str, Request] = {}
         self.steps = 0
         self.tokens_fed = 0
@@ -76,18 +77,31 @@ class Engine:
 
     def step(self) -> list[dict]:
         """Plan one batch, run it, sample, finish and free.  Returns the completions of this
-        step (they are also queued for ``drain_completed``)."""
+        step (they are also queued for ``drain_completed``).
+
+        While the GPU runs the step, the host already prepares the next one if it can be foreseen
+        (all running requests keep decoding): positions, pages and work lists do not depend on
+        the tokens being sampled; those are filled in when they arrive.  The plan itself always
+        comes from the scheduler; a prepared step is used only when it is exactly that plan."""
         plan = self.scheduler.schedule()
         if not plan.entries:
             return []
         entries = [StepEntry(e.request.request_id, e.tokens,
                              [len(e.tokens) - 1] if e.sample else []) for e in plan.entries]
-        sampling = [e.request for e in plan.entries if e.sample]
-        # the sampled token will sit at position num_computed + len(portion) = len(known tokens)
-        extra = pack_sampling([r.temperature for r in sampling], [r.seed for r in sampling],
-                              [r.num_tokens for r in sampling])
-        logits = self.runner.step(entries, extra)
-        tokens = self.sampler.sample(logits, self.runner.last_arrays)
+        ahead, self._ahead = self._ahead, None
+        if ahead is not None and self._same_step(ahead, entries):
+            prepared = ahead
+            self.runner.set_tokens(prepared, [e.tokens[0] for e in entries])
+        else:
+            sampling = [e.request for e in plan.entries if e.sample]
+            # the sampled token will sit at position num_computed + len(portion) = len(known tokens)
+            extra = pack_sampling([r.temperature for r in sampling], [r.seed for r in sampling],
+                                  [r.num_tokens for r in sampling])
+            prepared = self.runner.prepare(entries, extra)
+        logits = self.runner.launch(prepared)
+        self.sampler.launch(logits, self.runner.last_arrays)
+        self._ahead = self._prepare_ahead(plan)               # host work under the GPU's
+        tokens = self.sampler.wait()
         self.steps += 1
         self.tokens_fed += plan.num_tokens
         finished = self.scheduler.update(plan, tokens)
@@ -98,6 +112,36 @@ class Engine:
             self.requests.pop(request.request_id, None)
             done.append(record)
         return done
+
+    @staticmethod
+    def _same_step(prepared, entries: list[StepEntry]) -> bool:
+        mine = prepared.entries
+        return (len(mine) == len(entries)
+                and all(a.request_id == b.request_id and len(b.tokens) == 1 and b.want == [0]
+                        for a, b in zip(mine, entries)))
+
+    def _prepare_ahead(self, plan):
+        """The next step's host half, if it is sure to be one decoded token for every running
+        request: every running request samples in this step, none reaches its length limit,
+        nothing waits, and the pages are there.  An end-of-sequence token or anything else that
+        changes the plan simply leaves the prepared step unused."""
+        sched = self.scheduler
+        running = sched.running
+        if (sched.waiting or not running or len(plan.entries) != len(running)
+                or len(running) > sched.max_seqs or len(running) > sched.max_batch_tokens):
+            return None
+        for entry, request in zip(plan.entries, running):
+            if (entry.request is not request or not entry.sample
+                    or request.num_generated_tokens + 1 >= request.max_new_tokens):
+                return None
+        need = sum(self.cache.pages_needed(r.request_id, self.cache.length(r.request_id) + 1)
+                   for r in running)
+        if need > self.cache.num_free_pages():
+            return None
+        entries = [StepEntry(r.request_id, [0], [0]) for r in running]
+        extra = pack_sampling([r.temperature for r in running], [r.seed for r in running],
+                              [r.num_tokens + 1 for r in running])
+        return self.runner.prepare(entries, extra)
 
     def drain_completed(self) -> list[dict]:
         results = list(self.completed)

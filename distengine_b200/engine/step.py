@@ -34,6 +34,19 @@ class StepEntry:
     want: list[int] = field(default_factory=list)      # places among ``tokens``
 
 
+@dataclass
+class PreparedStep:
+    """A step whose host half is done (see ``StepRunner.prepare``)."""
+    entries: list
+    host: SimpleNamespace
+    prep: StepPrep
+    graph_shape: "dict | None"
+    fused: bool
+    views: dict
+    offsets: list
+    total: int
+
+
 class KernelStatusError(RuntimeError):
     """A kernel found an index it could not use (a position without a page) and skipped work."""
 
@@ -115,7 +128,9 @@ class StepRunner:
     _BASE = ("token_ids", "positions", "token_slot", "token_seq", "seq_slot", "seq_qstart",
              "seq_qlen", "seq_pos0", "logit_rows")
 
-    def _upload(self, host: SimpleNamespace, prep: StepPrep) -> StepContext:
+    def _stage(self, host: SimpleNamespace, prep: StepPrep) -> "tuple[dict, list, int, list]":
+        """Lay the step's arrays out in the pinned staging buffer.  Returns the device views, the
+        offsets, the number of ints and the arrays."""
         arrays = [(name, getattr(host, name)) for name in self._BASE]
         arrays += list(prep.extra.items())
         total = sum(_align(a.size) for _, a in arrays)
@@ -128,6 +143,7 @@ class StepRunner:
         self.upload_bytes = total * 4
         if self._upload_pending:
             self._uploaded.synchronize()          # the staging buffer is free again
+            self._upload_pending = False
         stage = self._host_meta.numpy()
         # where each array lies depends on the arrays' names and shapes only: keep the device
         # views of a layout (steady decoding repeats one layout step after step)
@@ -143,28 +159,15 @@ class StepRunner:
         views, offsets = layout
         for (name, array), offset in zip(arrays, offsets):
             stage[offset: offset + array.size] = array.reshape(-1)
-        self._dev_meta[:total].copy_(self._host_meta[:total], non_blocking=True)
-        self.cache.flush_tables()
-        self._uploaded.record()
-        self._upload_pending = True
-        return StepContext(
-            device=self.device, dtype=self.dtype, n_tokens=host.n_tokens, n_seqs=host.n_seqs,
-            token_ids=views["token_ids"], positions=views["positions"],
-            token_slot=views["token_slot"], token_seq=views["token_seq"],
-            seq_slot=views["seq_slot"], seq_qstart=views["seq_qstart"],
-            seq_qlen=views["seq_qlen"], seq_pos0=views["seq_pos0"],
-            logit_rows=views["logit_rows"], host=host,
-            arrays={k: v for k, v in views.items() if k not in self._BASE},
-            notes=prep.notes, workspace=self.workspace, status=self.status)
+        return views, offsets, total, arrays
 
     # ------------------------------------------------------------------ the step
-    def step(self, entries: list[StepEntry],
-             extra: "dict[str, np.ndarray] | None" = None) -> torch.Tensor:
-        """Run the entries as one batch.  ``extra``: int32 arrays of the caller's that travel to
-        the device with the step's own arrays (``self.last_arrays[name]`` afterwards).
-        Returns logits float32 [wanted, vocabulary] on the device, in the order of the entries and of each entry's ``want``; the tensor is reused by
-        the next step.  Raises ``OutOfPages`` (nothing changed) when the pool cannot hold the
-        step's tokens."""
+    def prepare(self, entries: list[StepEntry],
+                extra: "dict[str, np.ndarray] | None" = None) -> "PreparedStep":
+        """The host half of a step: validate, admit, take pages, build the step's arrays and lay
+        them out for upload.  Nothing is launched.  Only one prepared step may be outstanding: it
+        owns the staging buffer until ``launch`` (or until another ``prepare`` replaces it).
+        Raises ``OutOfPages`` (nothing changed) when the pool cannot hold the step's tokens."""
         self._validate(entries)
         admitted = []
         try:
@@ -192,19 +195,63 @@ class StepRunner:
             self.model.prepare(prep)
         for name, array in (extra or {}).items():
             prep.add(name, array)
-        ctx = self._upload(host, prep)
+        views, offsets, total, arrays = self._stage(host, prep)
+        return PreparedStep(entries, host, prep, graph_shape, fused, views, offsets, total)
+
+    def launch(self, prepared: "PreparedStep") -> torch.Tensor:
+        """The device half: upload the prepared arrays, run the model, advance the cache's
+        lengths.  Returns logits float32 [wanted, vocabulary] on the device, in the order of the
+        entries and of each entry's ``want``; the tensor is reused by the next step."""
+        host, prep, views = prepared.host, prepared.prep, prepared.views
+        total = prepared.total
+        self._dev_meta[:total].copy_(self._host_meta[:total], non_blocking=True)
+        self.cache.flush_tables()
+        self._uploaded.record()
+        self._upload_pending = True
+        ctx = StepContext(
+            device=self.device, dtype=self.dtype, n_tokens=host.n_tokens, n_seqs=host.n_seqs,
+            token_ids=views["token_ids"], positions=views["positions"],
+            token_slot=views["token_slot"], token_seq=views["token_seq"],
+            seq_slot=views["seq_slot"], seq_qstart=views["seq_qstart"],
+            seq_qlen=views["seq_qlen"], seq_pos0=views["seq_pos0"],
+            logit_rows=views["logit_rows"], host=host,
+            arrays={k: v for k, v in views.items() if k not in self._BASE},
+            notes=prep.notes, workspace=self.workspace, status=self.status)
         self.last_arrays = ctx.arrays
-        if fused:
+        if prepared.fused:
             logits = self.fused.run(ctx)
             self.fused_steps += 1
-        elif graph_shape is None:
+        elif prepared.graph_shape is None:
             logits = self.model.forward(ctx, self.bindings)
         else:
-            logits = self._forward_graphed(ctx, prep, graph_shape)
-        for e in entries:
+            logits = self._forward_graphed(ctx, prep, prepared.graph_shape)
+        for e in prepared.entries:
             self.cache.commit(e.request_id, self.cache.length(e.request_id) + len(e.tokens))
         self.steps_run += 1
         return logits
+
+    def step(self, entries: list[StepEntry],
+             extra: "dict[str, np.ndarray] | None" = None) -> torch.Tensor:
+        """Run the entries as one batch: ``prepare`` then ``launch``.  ``extra``: int32 arrays of
+        the caller's that travel to the device with the step's own arrays
+        (``self.last_arrays[name]`` afterwards)."""
+        return self.launch(self.prepare(entries, extra))
+
+    def set_tokens(self, prepared: "PreparedStep", tokens: list[int]) -> None:
+        """Put the token ids into a step that was prepared before they were known (one token per
+        entry): everything else of a decode step - positions, pages, work lists - does not depend
+        on them, so it can be prepared while the previous step still runs."""
+        if len(tokens) != prepared.host.n_tokens:
+            raise ValueError("one token for each token of the prepared step")
+        for t in tokens:
+            if type(t) is not int or not 0 <= t < self.vocabulary:
+                raise ValueError(f"token id {t} is outside the model vocabulary")
+        ids = np.asarray(tokens, dtype=np.int32)
+        prepared.host.token_ids = ids
+        offset = prepared.offsets[0]                       # token_ids is the first array
+        self._host_meta.numpy()[offset: offset + ids.size] = ids
+        for e, t in zip(prepared.entries, tokens):
+            e.tokens = [t]
 
     def _forward_graphed(self, ctx: StepContext, prep: StepPrep, graph_shape: dict) -> torch.Tensor:
         """Replay the decode step of this shape as a CUDA graph; the first step of a shape runs

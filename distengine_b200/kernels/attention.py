@@ -57,7 +57,9 @@ class AttentionLauncher:
         self.group = heads // kv_heads
         self.tensor_cores = uses_tensor_cores(dtype, head_dim)
         if self.tensor_cores:
-            self.shapes = [_Shape("wide", 64, 0), _Shape("narrow", NARROW_ROWS, 1)]
+            # wide tiles are 128 rows where the kernel gives a warp two row tiles (head size <= 64)
+            self.shapes = [_Shape("wide", 128 if head_dim <= 64 else 64, 0),
+                           _Shape("narrow", NARROW_ROWS, 1)]
             self.module = ("attention_mma", (f"HEAD_DIM={head_dim}",))
         else:
             self.shapes = [_Shape("rows8", 8, -1)]
@@ -163,6 +165,9 @@ def launch_items(code: int, module, q, out, k_pages, v_pages, block_table, seq_s
                     ("seq_pos0", seq_pos0), ("items", items)):
         _i32(t, name)
     lib = library.load(*module)
+    if code >= 0:
+        _need(lib.de_attn_mma_rows(code) == tile_rows,
+              "paged attention: the plan's tile height is not the kernel's")
     common = (q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), k_pages.data_ptr(),
               v_pages.data_ptr(), block_table.data_ptr(), block_table.stride(0),
               k_pages.shape[0], seq_slot.data_ptr(), seq_qstart.data_ptr(), seq_qlen.data_ptr(),

@@ -47,7 +47,7 @@ SIGNATURES: dict[str, dict[str, list]] = {
         "de_decode_fused_grid": [I], "de_decode_fused": [P, I, P],
     },
     "attention_mma": {
-        "de_attn_mma_head_dim": [],
+        "de_attn_mma_head_dim": [], "de_attn_mma_rows": [I],
         "de_attn_mma": [I, P, I, P, I, P, P, P, I, I, P, P, P, P, P, I, P, P, I, I, I, I, F, I, P],
     },
 }

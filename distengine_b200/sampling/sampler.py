@@ -32,12 +32,16 @@ class Sampler:
         self.device = device
         self.ids = torch.zeros(max_rows, dtype=torch.int32, device=device)
         self.host_ids = torch.zeros(max_rows, dtype=torch.int32).pin_memory()
+        self._done = torch.cuda.Event()
+        self._rows = 0
 
-    def sample(self, logits: torch.Tensor, arrays: "dict[str, torch.Tensor] | None") -> list[int]:
-        """Token ids for the rows of ``logits`` [R, V]; synchronises to bring them to the host."""
+    def launch(self, logits: torch.Tensor, arrays: "dict[str, torch.Tensor] | None") -> int:
+        """Start sampling the rows of ``logits`` [R, V] and the copy of the ids to the host;
+        returns R.  ``wait`` hands the ids out."""
         rows = logits.shape[0]
+        self._rows = rows
         if rows == 0:
-            return []
+            return 0
         if rows > self.ids.shape[0]:
             self.ids = torch.zeros(2 * rows, dtype=torch.int32, device=self.device)
             self.host_ids = torch.zeros(2 * rows, dtype=torch.int32).pin_memory()
@@ -49,5 +53,17 @@ class Sampler:
         else:
             ops.sample_rows(logits, out)
         self.host_ids[:rows].copy_(out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        return self.host_ids[:rows].tolist()
+        self._done.record()
+        return rows
+
+    def wait(self) -> list[int]:
+        """The ids of the last ``launch`` (synchronises with it)."""
+        if self._rows == 0:
+            return []
+        self._done.synchronize()
+        return self.host_ids[: self._rows].tolist()
+
+    def sample(self, logits: torch.Tensor, arrays: "dict[str, torch.Tensor] | None") -> list[int]:
+        """Token ids for the rows of ``logits`` [R, V]; synchronises to bring them to the host."""
+        self.launch(logits, arrays)
+        return self.wait()
