@@ -1,0 +1,329 @@
+// bfloat16 matrix product on the 5th-generation tensor cores: out[m, n] = sum_k x[m, k] * w[n, k],
+// float32 accumulation in tensor memory, for prompt portions (many rows of x).
+//
+// One block computes a 128 x BN tile of the output (BN = 128, or 64 + 64 with the gated epilogue):
+//   * a producer thread moves 128 x 64 tiles of x and BN x 64 tiles of w into shared memory with
+//     TMA (cp.async.bulk.tensor.2d, 128-byte swizzle, zero fill outside the matrices), STAGES deep,
+//     each stage guarded by a "full" mbarrier with a transaction count;
+//   * one thread issues tcgen05.mma (kind::f16, M = 128, N = BN, K = 16; operands are shared-memory
+//     descriptors, the accumulator lives in tensor memory), four per stage, and hands the stage back
+//     with tcgen05.commit on its "empty" mbarrier;
+//   * after the last stage a commit on the "done" mbarrier tells the four warps that the accumulator
+//     is complete; each warp reads its 32 lanes of tensor memory with tcgen05.ld, converts and
+//     stores its rows.  The gated epilogue computes silu(gate) * up from the two halves of the
+//     accumulator (src/layers/activation.py:6-9), so the activation costs no pass over memory.
+// No cluster launch, no multicast; every block fetches its own tiles.
+//
+// Every wait on an mbarrier is bounded: after SPIN_LIMIT polls a thread records status 3, stops
+// waiting, and the block runs to its end (tensor memory is freed on every path); the host raises.
+//
+// Stands where the reference calls F.linear (src/layers/linear.py:19-20) on [1, T, H] inputs.
+
+#include <cuda.h>
+
+#include "common.cuh"
+
+DE_DEFINE_PDL_SWITCH
+
+namespace {
+
+constexpr int BM = 128;                // rows of x per block = lanes of tensor memory
+constexpr int BN = 128;                // accumulator columns
+constexpr int BK = 64;                 // k per stage: 128 bytes of bfloat16 = one swizzle row
+constexpr int STAGES = 4;
+constexpr int THREADS = 128;
+constexpr int A_BYTES = BM * BK * 2;   // 16 KB
+constexpr int B_BYTES = BN * BK * 2;   // 16 KB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr unsigned SPIN_LIMIT = 20u * 1000u * 1000u;
+
+// ---------------------------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ unsigned smem_u32(const void* p) {
+    return (unsigned)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(void* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(void* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)),
+                 "r"(bytes) : "memory");
+}
+// Bounded wait for the phase with the given parity; false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity, int* status) {
+    const unsigned addr = smem_u32(bar);
+    for (unsigned spins = 0; spins < SPIN_LIMIT; ++spins) {
+        unsigned done;
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n"
+            "}\n"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    atomicExch(status, 3);
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, void* bar, int x,
+                                            int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4}], [%2];\n"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(void* smem_result, unsigned columns) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                 ::"r"(smem_u32(smem_result)), "r"(columns) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(unsigned taddr, unsigned columns) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "r"(columns)
+                 : "memory");
+}
+__device__ __forceinline__ void umma_bf16(unsigned d_tmem, unsigned long long a_desc,
+                                          unsigned long long b_desc, unsigned idesc, bool accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.u32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((unsigned)accumulate) : "memory");
+}
+// the mbarrier gets one arrival when every tcgen05.mma issued so far by this thread has finished
+__device__ __forceinline__ void umma_commit(void* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
+                 ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_load_32cols(unsigned taddr, float (&v)[32]) {
+    unsigned r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory operand descriptor: K-major tile of rows x 64 bfloat16 with the 128-byte swizzle.
+// start address / 16 in bits 0-13, leading byte offset / 16 in bits 16-29 (not used by swizzled
+// K-major layouts; 1), stride byte offset / 16 in bits 32-45 (from one group of 8 rows to the next:
+// 8 x 128 bytes), descriptor version 1 in bits 46-47, swizzle mode 2 (128 bytes) in bits 61-63.
+__device__ __forceinline__ unsigned long long smem_desc(const void* tile) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((smem_u32(tile) & 0x3FFFF) >> 4);
+    d |= (unsigned long long)1 << 16;
+    d |= (unsigned long long)(1024 >> 4) << 32;
+    d |= (unsigned long long)1 << 46;
+    d |= (unsigned long long)2 << 61;
+    return d;
+}
+// Instruction descriptor, kind::f16: float32 accumulator (bits 4-5 = 1), bfloat16 a and b (bits
+// 7-9 and 10-12 = 1), both K-major (bits 15, 16 = 0), N / 8 in bits 17-22, M / 16 in bits 24-28.
+__host__ __device__ constexpr unsigned instr_desc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) |
+           ((unsigned)(m >> 4) << 24);
+}
+
+// GATED: the accumulator's columns 0..63 are gate outputs, 64..127 the up outputs of the same 64
+// features; the block writes 64 columns of silu(gate) * up.
+template <bool GATED, typename OutT>
+__global__ void __launch_bounds__(THREADS)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
+                    const __grid_constant__ CUtensorMap map_w, OutT* __restrict__ out, int ldo,
+                    int m_rows, int n_out, int k_dim, int up_row_offset, int* status) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    // the tiles need 1024-byte alignment for the swizzle pattern
+    unsigned char* tiles = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES], done_bar;
+    __shared__ unsigned tmem_base_slot;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile_n = blockIdx.x, tile_m = blockIdx.y;
+    const int k_steps = (k_dim + BK - 1) / BK;
+    constexpr int OUT_COLS = GATED ? BN / 2 : BN;         // output columns of a block
+
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(&done_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 2) tmem_alloc(&tmem_base_slot, BN);        // BN columns of float32, 128 lanes
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const unsigned tmem_base = tmem_base_slot;
+
+    pdl_wait();                                            // x is the previous kernel's output
+    bool ok = true;
+    if (warp == 0 && lane == 0) {
+        // ---- producer: TMA loads, one stage ahead of the tensor core by up to STAGES
+        for (int ks = 0; ks < k_steps && ok; ++ks) {
+            const int s = ks % STAGES;
+            if (ks >= STAGES) ok = mbar_wait(&empty_bar[s], ((ks / STAGES) - 1) & 1, status);
+            if (!ok) break;
+            unsigned char* a_tile = tiles + s * STAGE_BYTES;
+            unsigned char* b_tile = a_tile + A_BYTES;
+            mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+            tma_load_2d(a_tile, &map_x, &full_bar[s], ks * BK, tile_m * BM);
+            if (GATED) {
+                tma_load_2d(b_tile, &map_w, &full_bar[s], ks * BK, tile_n * (BN / 2));
+                tma_load_2d(b_tile + B_BYTES / 2, &map_w, &full_bar[s], ks * BK,
+                            up_row_offset + tile_n * (BN / 2));
+            } else {
+                tma_load_2d(b_tile, &map_w, &full_bar[s], ks * BK, tile_n * BN);
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- tensor core: four K = 16 steps per stage, accumulator in tensor memory
+        constexpr unsigned idesc = instr_desc(BM, BN);
+        for (int ks = 0; ks < k_steps && ok; ++ks) {
+            const int s = ks % STAGES;
+            ok = mbar_wait(&full_bar[s], (ks / STAGES) & 1, status);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const unsigned char* a_tile = tiles + s * STAGE_BYTES;
+            const unsigned long long a_desc = smem_desc(a_tile);
+            const unsigned long long b_desc = smem_desc(a_tile + A_BYTES);
+#pragma unroll
+            for (int k = 0; k < BK / 16; ++k) {
+                // 16 elements of k are 32 bytes: the descriptors' start addresses advance by 2
+                umma_bf16(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, ks > 0 || k > 0);
+            }
+            umma_commit(&empty_bar[s]);                    // the stage is free when these are done
+        }
+        umma_commit(&done_bar);
+    }
+    __syncwarp();
+
+    // ---- epilogue: every warp reads its 32 lanes of the accumulator
+    pdl_trigger();
+    const bool finished = mbar_wait(&done_bar, 0, status);
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const int row = tile_m * BM + warp * 32 + lane;
+    if (finished) {
+        const unsigned lane_base = tmem_base + ((unsigned)(warp * 32) << 16);
+        if (GATED) {
+#pragma unroll 1
+            for (int c = 0; c < BN / 2; c += 32) {
+                float gate[32], up[32];
+                tmem_load_32cols(lane_base + c, gate);
+                tmem_load_32cols(lane_base + BN / 2 + c, up);
+                if (row < m_rows) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int col = tile_n * OUT_COLS + c + i;
+                        if (col < n_out) {
+                            const float g = __bfloat162float(__float2bfloat16_rn(gate[i]));
+                            const float u = __bfloat162float(__float2bfloat16_rn(up[i]));
+                            out[(size_t)row * ldo + col] = from_float<OutT>(g / (1.0f + expf(-g)) * u);
+                        }
+                    }
+                }
+            }
+        } else {
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                float v[32];
+                tmem_load_32cols(lane_base + c, v);
+                if (row < m_rows) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int col = tile_n * OUT_COLS + c + i;
+                        if (col < n_out) out[(size_t)row * ldo + col] = from_float<OutT>(v[i]);
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 2) tmem_dealloc(tmem_base, BN);
+}
+
+// ---------------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+    static EncodeTiled fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+                cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiled>(p);
+    }
+    return fn;
+}
+
+// A [rows, k] bfloat16 matrix with row stride ld (elements), boxes of box_rows x 64.
+int make_map(CUtensorMap* map, const void* base, int rows, int k, int ld, int box_rows) {
+    EncodeTiled encode = encode_fn();
+    if (encode == nullptr) return -20;
+    cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base),
+                              dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : -21;
+}
+
+template <bool GATED, typename OutT>
+int launch(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int m_rows, int n_out,
+           int k_dim, int* status, cudaStream_t s) {
+    CUtensorMap map_x, map_w;
+    int code = make_map(&map_x, x, m_rows, k_dim, ldx, BM);
+    if (code) return code;
+    code = make_map(&map_w, w, GATED ? 2 * n_out : n_out, k_dim, ldw, GATED ? BN / 2 : BN);
+    if (code) return code;
+    const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024;
+    auto kernel = gemm_tcgen05_kernel<GATED, OutT>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    const int out_cols = GATED ? BN / 2 : BN;
+    dim3 grid((n_out + out_cols - 1) / out_cols, (m_rows + BM - 1) / BM);
+    return de_launch(kernel, grid, dim3(THREADS), smem, s, map_x, map_w, (OutT*)out, ldo, m_rows,
+                     n_out, k_dim, n_out, status);
+}
+
+}  // namespace
+
+// out_f32: float32 output (not with gated).  gated: w is [2 n_out, k] with the gate rows first; out
+// is [m, n_out] = silu(x gate^T) * (x up^T).  x, w: bfloat16, rows contiguous, 16-byte aligned
+// row starts.  `status` receives 3 if a wait inside the kernel ran out.
+DE_EXPORT int de_gemm_tcgen05(const void* x, int ldx, const void* w, int ldw, void* out, int ldo,
+                              int m_rows, int n_out, int k_dim, int out_f32, int gated, int* status,
+                              void* stream) {
+    if (m_rows <= 0 || n_out <= 0) return 0;
+    if (k_dim <= 0 || k_dim % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || ((uintptr_t)x & 15) ||
+        ((uintptr_t)w & 15))
+        return -3;
+    if (gated && n_out % (BN / 2) != 0) return -4;         // a gate tile must not run into up rows
+    cudaStream_t s = (cudaStream_t)stream;
+    if (gated) {
+        if (out_f32) return -5;
+        return launch<true, __nv_bfloat16>(x, ldx, w, ldw, out, ldo, m_rows, n_out, k_dim, status, s);
+    }
+    if (out_f32) return launch<false, float>(x, ldx, w, ldw, out, ldo, m_rows, n_out, k_dim, status, s);
+    return launch<false, __nv_bfloat16>(x, ldx, w, ldw, out, ldo, m_rows, n_out, k_dim, status, s);
+}

@@ -33,6 +33,7 @@ MODULES: dict[str, tuple[str, tuple[str, ...]]] = {
     "gemm_f32": ("gemm_f32.cu", ()),
     "attention_simt": ("attention_simt.cu", ()),
     "linear_small": ("linear_small.cu", ()),
+    "gemm_tcgen05": ("gemm_tcgen05.cu", ()),
     "attention_mma": ("attention_mma.cu", ()),          # built per head size: HEAD_DIM=<d>
     "decode_fused": ("decode_fused.cu", ()),            # built per head size: HEAD_DIM=<d>
 }

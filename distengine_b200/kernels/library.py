@@ -41,6 +41,9 @@ SIGNATURES: dict[str, dict[str, list]] = {
         "de_linear_small_max_rows": [],
         "de_linear_small": [P, I, P, I, P, I, I, I, I, I, I, P],
     },
+    "gemm_tcgen05": {
+        "de_gemm_tcgen05": [P, I, P, I, P, I, I, I, I, I, I, P, P],
+    },
     "decode_fused": {
         "de_decode_fused_head_dim": [], "de_decode_fused_max_tokens": [],
         "de_decode_fused_args_bytes": [], "de_decode_fused_layer_bytes": [],

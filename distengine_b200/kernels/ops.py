@@ -218,6 +218,34 @@ def linear_gated(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor,
     return out
 
 
+_tcgen05_status: "torch.Tensor | None" = None
+
+
+def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated: bool = False,
+                 status: "torch.Tensor | None" = None) -> torch.Tensor:
+    """out = x @ w^T on the 5th-generation tensor cores (``csrc/gemm_tcgen05.cu``: TMA loads,
+    tcgen05.mma with the accumulator in tensor memory), bfloat16 operands, bfloat16 or float32
+    output.  ``gated``: w = [gate rows; up rows] ([2 n, k]) and out [m, n] = silu(gate) * up.
+    ``status`` (int32 [1]) receives 3 if a wait inside the kernel ran out."""
+    global _tcgen05_status
+    n = w.shape[0] // 2 if gated else w.shape[0]
+    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2
+          and w.dim() == 2 and x.shape[1] == w.shape[1] and tuple(out.shape) == (x.shape[0], n)
+          and x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1,
+          "gemm_tcgen05: x [m, k] and w [n, k] bfloat16 with contiguous rows, out [m, n]")
+    _need(out.dtype in (torch.bfloat16, torch.float32), "gemm_tcgen05: out bfloat16 or float32")
+    if status is None:
+        if _tcgen05_status is None or _tcgen05_status.device != x.device:
+            _tcgen05_status = torch.zeros(1, dtype=torch.int32, device=x.device)
+        status = _tcgen05_status
+    lib = library.load("gemm_tcgen05")
+    _check(lib.de_gemm_tcgen05(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0),
+                               out.data_ptr(), out.stride(0), x.shape[0], n, x.shape[1],
+                               int(out.dtype == torch.float32), int(gated), status.data_ptr(),
+                               _stream()), "gemm_tcgen05")
+    return out
+
+
 # ------------------------------------------------------------------------------- sampling
 def sample_rows(logits: torch.Tensor, out: torch.Tensor,
                 temperature: "torch.Tensor | None" = None, seed: "torch.Tensor | None" = None,
