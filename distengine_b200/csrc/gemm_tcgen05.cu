@@ -30,7 +30,8 @@ namespace {
 constexpr int BM = 128;                // rows of x per block = lanes of tensor memory
 constexpr int BN = 128;                // accumulator columns
 constexpr int BK = 64;                 // k per stage: 128 bytes of bfloat16 = one swizzle row
-constexpr int STAGES = 4;
+constexpr int STAGES = 3;                // 96 KB of tiles: two blocks fit an SM, so one block's
+                                        // epilogue runs under the other's main loop
 constexpr int THREADS = 128;
 constexpr int A_BYTES = BM * BK * 2;   // 16 KB
 constexpr int B_BYTES = BN * BK * 2;   // 16 KB
@@ -72,6 +73,10 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, v
         "[%0], [%1, {%3, %4}], [%2];\n"
         ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
 }
+__device__ __forceinline__ unsigned pack2(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const unsigned*>(&v);
+}
 __device__ __forceinline__ void tmem_alloc(void* smem_result, unsigned columns) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
                  ::"r"(smem_u32(smem_result)), "r"(columns) : "memory");
@@ -96,8 +101,11 @@ __device__ __forceinline__ void umma_commit(void* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
                  ::"r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ void tmem_load_32cols(unsigned taddr, float (&v)[32]) {
-    unsigned r[32];
+__device__ __forceinline__ void tmem_wait_loads() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+// 32 consecutive columns of this thread's lane; the values are valid after tmem_wait_loads()
+__device__ __forceinline__ void tmem_load_32cols(unsigned taddr, unsigned (&r)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -108,9 +116,17 @@ __device__ __forceinline__ void tmem_load_32cols(unsigned taddr, float (&v)[32])
           "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
           "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// 8 consecutive outputs as one 16-byte store (bfloat16) or two (float32)
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&v)[8]) {
+    uint4 u;
+    u.x = pack2(v[0], v[1]); u.y = pack2(v[2], v[3]); u.z = pack2(v[4], v[5]); u.w = pack2(v[6], v[7]);
+    *reinterpret_cast<uint4*>(p) = u;
+}
+__device__ __forceinline__ void store8(float* p, const float (&v)[8]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
 }
 
 // Shared-memory operand descriptor: K-major tile of rows x 64 bfloat16 with the 128-byte swizzle.
@@ -216,35 +232,65 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
     const int row = tile_m * BM + warp * 32 + lane;
     if (finished) {
         const unsigned lane_base = tmem_base + ((unsigned)(warp * 32) << 16);
+        // rows whose 8-column groups can go out as 16-byte stores
+        const bool vec = (ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
+        OutT* out_row = out + (size_t)row * ldo + tile_n * OUT_COLS;
+        const int cols_left = n_out - tile_n * OUT_COLS;          // valid columns of this tile
         if (GATED) {
 #pragma unroll 1
             for (int c = 0; c < BN / 2; c += 32) {
-                float gate[32], up[32];
+                unsigned gate[32], up[32];
                 tmem_load_32cols(lane_base + c, gate);
                 tmem_load_32cols(lane_base + BN / 2 + c, up);
+                tmem_wait_loads();
                 if (row < m_rows) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int col = tile_n * OUT_COLS + c + i;
-                        if (col < n_out) {
-                            const float g = __bfloat162float(__float2bfloat16_rn(gate[i]));
-                            const float u = __bfloat162float(__float2bfloat16_rn(up[i]));
-                            out[(size_t)row * ldo + col] = from_float<OutT>(g / (1.0f + expf(-g)) * u);
+                    for (int i = 0; i < 32; i += 8) {
+                        float y[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            // product outputs are rounded to bfloat16 before the activation, as a
+                            // separate product and activation kernel would do
+                            const float g = __bfloat162float(__float2bfloat16_rn(
+                                __uint_as_float(gate[i + j])));
+                            const float u = __bfloat162float(__float2bfloat16_rn(
+                                __uint_as_float(up[i + j])));
+                            y[j] = g / (1.0f + __expf(-g)) * u;
+                        }
+                        if (vec && c + i + 8 <= cols_left) {
+                            store8(out_row + c + i, y);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                if (c + i + j < cols_left) out_row[c + i + j] = from_float<OutT>(y[j]);
                         }
                     }
                 }
             }
         } else {
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
-                float v[32];
-                tmem_load_32cols(lane_base + c, v);
+            for (int c = 0; c < BN; c += 64) {
+                unsigned v[2][32];
+                tmem_load_32cols(lane_base + c, v[0]);
+                tmem_load_32cols(lane_base + c + 32, v[1]);
+                tmem_wait_loads();
                 if (row < m_rows) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int col = tile_n * OUT_COLS + c + i;
-                        if (col < n_out) out[(size_t)row * ldo + col] = from_float<OutT>(v[i]);
-                    }
+                    for (int h = 0; h < 2; ++h)
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            float y[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) y[j] = __uint_as_float(v[h][i + j]);
+                            const int col = c + 32 * h + i;
+                            if (vec && col + 8 <= cols_left) {
+                                store8(out_row + col, y);
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 8; ++j)
+                                    if (col + j < cols_left) out_row[col + j] = from_float<OutT>(y[j]);
+                            }
+                        }
                 }
             }
         }

@@ -369,3 +369,37 @@ def test_linear_gated(m, k, inner):
     gate = plain.plain_linear(x.float(), w[:inner].float(), torch.bfloat16)
     up = plain.plain_linear(x.float(), w[inner:].float(), torch.bfloat16)
     assert_close(out, plain.plain_swiglu(gate, up, torch.bfloat16), torch.bfloat16, "linear_gated")
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (77, 200, 120), (300, 384, 2048), (129, 331 + 5, 72),
+                                   (2048, 256, 5632), (33, 50, 8)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_tcgen05(m, n, k, out_dtype):
+    """The tensor-memory matrix product (TMA + tcgen05.mma) at sizes that are no multiples of its
+    tiles; a poisoned output shows rows or columns it would skip."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(m + n + k)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(n, k, generator=g) * 0.1).to(torch.bfloat16)
+    out = torch.full((m, n), float("nan"), dtype=out_dtype, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.gemm_tcgen05(x.to(DEV), w.to(DEV), out, status=status)
+    assert status.item() == 0
+    want = plain.plain_linear(x.float(), w.float(), torch.bfloat16, keep_f32=out_dtype == torch.float32)
+    assert_close(out, want, out_dtype, "gemm_tcgen05")
+
+
+@pytest.mark.parametrize("m,inner,k", [(128, 64, 64), (200, 192, 120), (2048, 5632, 2048), (40, 320, 264)])
+def test_gemm_tcgen05_gated(m, inner, k):
+    """silu(gate) * up as the epilogue of the tensor-memory product."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(m + inner + k)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(2 * inner, k, generator=g) * 0.1).to(torch.bfloat16)
+    out = torch.full((m, inner), float("nan"), dtype=torch.bfloat16, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.gemm_tcgen05(x.to(DEV), w.to(DEV), out, gated=True, status=status)
+    assert status.item() == 0
+    gate = plain.plain_linear(x.float(), w[:inner].float(), torch.bfloat16)
+    up = plain.plain_linear(x.float(), w[inner:].float(), torch.bfloat16)
+    assert_close(out, plain.plain_swiglu(gate, up, torch.bfloat16), torch.bfloat16, "gated tcgen05")
