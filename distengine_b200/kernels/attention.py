@@ -19,11 +19,14 @@ from dataclasses import dataclass
 import numpy as np
 import torch
 
+import os
+
 from . import library
 from .attention_plan import build_plan, choose_chunk
 from .ops import _check, _i32, _need, _ptr, _stream, _tag
 
 MAX_HEAD_DIM = 256
+_status_fallback: "torch.Tensor | None" = None
 NARROW_ROWS = 16
 
 
@@ -61,6 +64,10 @@ class AttentionLauncher:
             self.shapes = [_Shape("wide", 128 if head_dim <= 64 else 64, 0),
                            _Shape("narrow", NARROW_ROWS, 1)]
             self.module = ("attention_mma", (f"HEAD_DIM={head_dim}",))
+            # prompt portions at head size 64: the tcgen05 kernel (tensor-memory accumulators, TMA
+            # page loads) takes the wide tiles; DISTENGINE_B200_ATTENTION=mma keeps the mma.sync one
+            if head_dim == 64 and os.environ.get("DISTENGINE_B200_ATTENTION", "tcgen05") != "mma":
+                self.shapes[0] = _Shape("wide", 128, 2)
         else:
             self.shapes = [_Shape("rows8", 8, -1)]
             self.module = ("attention_simt", ())
@@ -152,21 +159,26 @@ class AttentionLauncher:
                 rows = num_partials * self.kv_heads * shape.rows
                 acc = ctx.buffer(f"attention.partial_acc.{shape.name}", (rows * d,), torch.float32)
                 ml = ctx.buffer(f"attention.partial_ml.{shape.name}", (rows * 2,), torch.float32)
-            launch_items(shape.code, self.module, q, out, k_pages, v_pages, block_table,
+            module = ("attention_tcgen05", ()) if shape.code == 2 else self.module
+            launch_items(shape.code, module, q, out, k_pages, v_pages, block_table,
                          ctx.seq_slot, ctx.seq_qstart, ctx.seq_qlen, ctx.seq_pos0, items, combine,
-                         shape.rows, acc, ml, self.heads, self.kv_heads, d, self.scale, self.window)
+                         shape.rows, acc, ml, self.heads, self.kv_heads, d, self.scale, self.window,
+                         getattr(ctx, "status", None))
 
 
 def launch_items(code: int, module, q, out, k_pages, v_pages, block_table, seq_slot, seq_qstart,
                  seq_qlen, seq_pos0, items, combine, tile_rows, partial_acc, partial_ml, heads,
-                 kv_heads, head_dim, scale, window) -> None:
+                 kv_heads, head_dim, scale, window, status=None) -> None:
     """One launch of a kernel over ``items`` and, if any range was split, the merge."""
     for name, t in (("seq_slot", seq_slot), ("seq_qstart", seq_qstart), ("seq_qlen", seq_qlen),
                     ("seq_pos0", seq_pos0), ("items", items)):
         _i32(t, name)
     lib = library.load(*module)
-    if code >= 0:
+    if code in (0, 1):
         _need(lib.de_attn_mma_rows(code) == tile_rows,
+              "paged attention: the plan's tile height is not the kernel's")
+    elif code == 2:
+        _need(lib.de_attn_tcgen05_rows() == tile_rows,
               "paged attention: the plan's tile height is not the kernel's")
     common = (q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), k_pages.data_ptr(),
               v_pages.data_ptr(), block_table.data_ptr(), block_table.stride(0),
@@ -176,6 +188,14 @@ def launch_items(code: int, module, q, out, k_pages, v_pages, block_table, seq_s
               int(window or 0), _stream())
     if code < 0:
         _check(lib.de_attn_simt(_tag(q.dtype), *common), "paged attention")
+    elif code == 2:
+        global _status_fallback
+        if status is None:
+            if _status_fallback is None or _status_fallback.device != q.device:
+                _status_fallback = torch.zeros(1, dtype=torch.int32, device=q.device)
+            status = _status_fallback
+        _check(lib.de_attn_tcgen05(*common[:-1], status.data_ptr(), common[-1]),
+               "paged attention (tcgen05)")
     else:
         _check(lib.de_attn_mma(code, *common), "paged attention (tensor cores)")
     if combine is not None and combine.shape[0] > 0:

@@ -35,6 +35,7 @@ MODULES: dict[str, tuple[str, tuple[str, ...]]] = {
     "linear_small": ("linear_small.cu", ()),
     "gemm_tcgen05": ("gemm_tcgen05.cu", ()),
     "attention_mma": ("attention_mma.cu", ()),          # built per head size: HEAD_DIM=<d>
+    "attention_tcgen05": ("attention_tcgen05.cu", ()),  # head size 64
     "decode_fused": ("decode_fused.cu", ()),            # built per head size: HEAD_DIM=<d>
 }
 

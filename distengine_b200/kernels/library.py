@@ -49,6 +49,10 @@ SIGNATURES: dict[str, dict[str, list]] = {
         "de_decode_fused_args_bytes": [], "de_decode_fused_layer_bytes": [],
         "de_decode_fused_grid": [I], "de_decode_fused": [P, I, P],
     },
+    "attention_tcgen05": {
+        "de_attn_tcgen05_rows": [], "de_attn_tcgen05_head_dim": [],
+        "de_attn_tcgen05": [P, I, P, I, P, P, P, I, I, P, P, P, P, P, I, P, P, I, I, I, I, F, I, P, P],
+    },
     "attention_mma": {
         "de_attn_mma_head_dim": [], "de_attn_mma_rows": [I],
         "de_attn_mma": [I, P, I, P, I, P, P, P, I, I, P, P, P, P, P, I, P, P, I, I, I, I, F, I, P],
@@ -61,7 +65,7 @@ _loaded: dict[tuple[str, tuple[str, ...]], ctypes.CDLL] = {}
 def default_build_requests() -> list[tuple[str, tuple[str, ...]]]:
     """Every module; the per-head-size attention for the head sizes of common models."""
     requests = [(module, ()) for module in _build.MODULES
-                if module in SIGNATURES and module not in ("attention_mma", "decode_fused")]
+                if module in SIGNATURES and module not in ("attention_mma", "decode_fused")]  # noqa
     return (requests + [("attention_mma", (f"HEAD_DIM={d}",)) for d in (64, 128)]
             + [("decode_fused", (f"HEAD_DIM={d}",)) for d in (64, 128)])
 
