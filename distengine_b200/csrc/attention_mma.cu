@@ -101,12 +101,13 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16
     __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);        // [2][KT][LDS]
     __nv_bfloat16* v_s = k_s + 2 * KT * LDS;                                  // [2][KT][LDS]
 
-    const WorkItem it = items[blockIdx.x];
+    // blocks are numbered item-major, so that the items run in the order the host gave them
+    const WorkItem it = items[blockIdx.x / kv_heads];
     if (it.kv_begin >= it.kv_end) {                                           // padding item
         pdl_wait();
         return;
     }
-    const int hk = blockIdx.y;
+    const int hk = blockIdx.x % kv_heads;
     const int g = heads / kv_heads;
     const int qlen = seq_qlen[it.seq], pos0 = seq_pos0[it.seq];
     const int slot = seq_slot[it.seq], tok0 = seq_qstart[it.seq];
@@ -414,7 +415,7 @@ int launch(const void* q, int q_stride, void* out, int out_stride, const void* k
                                              (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    dim3 grid(num_items, kv_heads);
+    dim3 grid((unsigned)num_items * (unsigned)kv_heads);
     return de_launch(kernel, grid, dim3(THREADS), smem, s, (const __nv_bfloat16*)q, q_stride,
                      (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pages,
                      (const __nv_bfloat16*)v_pages, block_table, table_stride, num_pages, seq_slot,

@@ -3,7 +3,8 @@
 //
 // The same work items as attention_mma.cu's wide shape: a tile of 128 query rows of one sequence
 // and one kv head (rows are (token, query head of the group)) with a range of key positions.
-// A block of 128 threads owns the tile: thread i owns row i, which is lane i of tensor memory.
+// A block of 256 threads owns the tile: row i is lane i of tensor memory, and two threads (in warps
+// w and w + 4, which may both read that lane) each serve half of its columns.
 // For every tile of 128 keys:
 //   1. thread 0 waits for the K and V pages of the tile (one TMA box per page, 128-byte swizzle,
 //      straight from the page pool through the block table) and issues s = q k^T: four
@@ -15,9 +16,9 @@
 //      "MN-major" operand, i.e. exactly as the cache stores it ([key][feature]);
 //   4. every thread reads its row of o_tile and adds it to its float32 output row, scaled by the
 //      change of the running maximum.
-// While a tile is worked on, the pages of the next one are in flight (two stages).  Two blocks
-// fit an SM (112 KB of shared memory, 256 of 512 tensor-memory columns each), so the softmax of
-// one overlaps the matrix products of the other.
+// The tensor core runs ahead: s of the next tile is issued (into a second buffer in tensor memory)
+// before the softmax of the current one starts, and the pages are fetched two tiles ahead (three
+// stages).  One block per SM (145 KB of shared memory, all 512 tensor-memory columns).
 //
 // Formulas as in src/layers/attention.py:35-71 (scale after the product, causal mask, float32
 // softmax), grouped-query heads share the kv head's tiles.  Split key ranges write partial
@@ -37,12 +38,12 @@ namespace {
 constexpr int D = 64;                  // head size: 128 bytes of bfloat16 = one swizzle row
 constexpr int ROWS = 128;              // query rows of a tile = lanes of tensor memory
 constexpr int KT = 128;                // keys per tile
-constexpr int THREADS = 128;
+constexpr int THREADS = 320;            // 8 softmax warps (two threads a row), tensor-core warp, copy warp
+constexpr int STAGES = 3;               // key/value tiles in flight
 constexpr int TILE_BYTES = 128 * 128;  // 128 rows of 128 bytes
-constexpr int TMEM_COLS = 256;         // s: 0..127, o_tile: 128..191
+constexpr int TMEM_COLS = 512;         // s buffers at 0 and 128, p v buffers at 256 and 320
 constexpr unsigned SPIN_LIMIT = 20u * 1000u * 1000u;
-constexpr int PAGE_CACHE = 192;        // block-table entries kept in shared memory
-constexpr int SMEM_BYTES = 7 * TILE_BYTES + 48 + PAGE_CACHE * 4;
+constexpr int SMEM_BYTES = (1 + 2 * STAGES + 4) * TILE_BYTES + 128 + 2048;
 #ifndef V_DESC_SWAP
 #define V_DESC_SWAP 0
 #endif
@@ -61,6 +62,9 @@ __device__ __forceinline__ void mbar_init(void* bar, unsigned count) {
 __device__ __forceinline__ void mbar_expect_tx(void* bar, unsigned bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)),
                  "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(void* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity, int* status) {
     const unsigned addr = smem_u32(bar);
@@ -128,6 +132,22 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool pr
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(smem)), "l"(gmem),
                  "r"(bytes));
 }
+#ifdef ATTN_TIMING
+// Debugging aid, compiled on request only: wall-clock stamps of one block's phases.
+__device__ unsigned long long attn_stamps[2 * 64 * 8];
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
+    return t;
+}
+#define STAMP(who, tile, k)                                                                  \
+    do {                                                                                     \
+        if (blockIdx.x == ATTN_TIMING && (tile) < 64)                                        \
+            attn_stamps[((who) * 64 + (tile)) * 8 + (k)] = global_ns();                      \
+    } while (0)
+#else
+#define STAMP(who, tile, k) do { } while (0)
+#endif
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
@@ -172,7 +192,7 @@ __host__ __device__ constexpr unsigned instr_desc(int m, int n, bool b_mn_major)
            ((unsigned)(n >> 3) << 17) | ((unsigned)(m >> 4) << 24);
 }
 
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 1)
 attn_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* __restrict__ out,
                     int out_stride, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table,
@@ -182,48 +202,59 @@ attn_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
                     float* __restrict__ partial_acc, float* __restrict__ partial_ml, int heads,
                     int kv_heads, int page, float scale, int window, int* status) {
     // All shared memory is dynamic and starts at the block's window (1024-byte aligned, which the
-    // swizzled tiles need; checked below): seven tiles, then barriers, the tensor-memory address
-    // and the block-table entries of this item's key range.  Two blocks fit an SM.
+    // swizzled tiles need; checked below).
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* q_s = smem_raw;                               // 16 KB
-    unsigned char* k_s = q_s + TILE_BYTES;                       // 2 x 16 KB
-    unsigned char* v_s = k_s + 2 * TILE_BYTES;                   // 2 x 16 KB
-    unsigned char* p_s = v_s + 2 * TILE_BYTES;                   // 2 sub-tiles of 128 rows x 64 keys
-    unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem_raw + 7 * TILE_BYTES);
-    unsigned long long* kv_full = bars;                          // [2]
-    unsigned long long& s_done = bars[2];
-    unsigned long long& o_done = bars[3];
-    unsigned& tmem_slot = *reinterpret_cast<unsigned*>(bars + 4);
-    int* page_ids = reinterpret_cast<int*>(bars + 6);            // [PAGE_CACHE]
+    unsigned char* k_s = q_s + TILE_BYTES;                       // STAGES x 16 KB
+    unsigned char* v_s = k_s + STAGES * TILE_BYTES;              // STAGES x 16 KB
+    unsigned char* p_s = v_s + STAGES * TILE_BYTES;              // 2 buffers x 2 sub-tiles (128 x 64 keys)
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(p_s + 4 * TILE_BYTES);
+    unsigned long long* kv_full = bars;                          // [STAGES] pages of a tile have landed
+    unsigned long long* s_done = bars + STAGES;                  // [2] scores are in tensor memory
+    unsigned long long* p_ready = bars + STAGES + 2;             // [2] p is in shared memory (256 arrivals)
+    unsigned long long* o_done = bars + STAGES + 4;              // [2] p v is in tensor memory
+    unsigned long long* o_free = bars + STAGES + 6;              // [2] p v has been read (256 arrivals)
+    unsigned& tmem_slot = *reinterpret_cast<unsigned*>(bars + STAGES + 8);
+    float* xch = reinterpret_cast<float*>(bars + STAGES + 9);    // [2][128] row values between halves
 
-    const WorkItem it = items[blockIdx.x];
+    // blocks are numbered item-major, so that the items run in the order the host gave them
+    const WorkItem it = items[blockIdx.x / kv_heads];
     if (it.kv_begin >= it.kv_end || (smem_u32(smem_raw) & 1023u) != 0) {   // padding item
         if ((smem_u32(smem_raw) & 1023u) != 0 && threadIdx.x == 0) atomicExch(status, 4);
         pdl_wait();
         return;
     }
+    // Warps 0..7 are the softmax threads: thread (warp w, lane l) serves row 32 (w % 4) + l - the
+    // lane of tensor memory its warp may read - and the half w / 4 of that row's columns.  Warp 8
+    // issues the tensor-core work, warp 9 the copies.
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int hk = blockIdx.y;
+    const bool driver = warp >= 8;
+    const int rowi = (warp & 3) * 32 + lane, half = (warp >> 2) & 1;
+    const int hk = blockIdx.x % kv_heads;
     const int g = heads / kv_heads;
     const int qlen = seq_qlen[it.seq], pos0 = seq_pos0[it.seq];
     const int slot = seq_slot[it.seq], tok0 = seq_qstart[it.seq];
     const int rows_total = qlen * g;
 
     if (tid == 0) {
-        mbar_init(&kv_full[0], 1);
-        mbar_init(&kv_full[1], 1);
-        mbar_init(&s_done, 1);
-        mbar_init(&o_done, 1);
+#pragma unroll
+        for (int i = 0; i < STAGES; ++i) mbar_init(&kv_full[i], 1);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&s_done[i], 1);
+            mbar_init(&p_ready[i], 256);
+            mbar_init(&o_done[i], 1);
+            mbar_init(&o_free[i], 256);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    if (warp == 1) tmem_alloc(&tmem_slot, TMEM_COLS);
+    if (warp == 8) tmem_alloc(&tmem_slot, TMEM_COLS);
     // stale shared memory must be finite: p = 0 times a NaN bit pattern would poison the product
-    for (int i = tid; i < 4 * TILE_BYTES / 16; i += THREADS)
+    for (int i = tid; i < 2 * STAGES * TILE_BYTES / 16; i += THREADS)
         reinterpret_cast<uint4*>(k_s)[i] = make_uint4(0u, 0u, 0u, 0u);
 
-    // this thread's row
-    const int r = it.row0 + tid;
-    const bool live = r < rows_total;
+    const int r = it.row0 + rowi;
+    const bool live = !driver && r < rows_total;
     const int tok = live ? r / g : 0;
     const int hq = hk * g + (live ? r % g : 0);
     const int pos = live ? pos0 + tok : -1;
@@ -240,20 +271,14 @@ attn_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
     const int hi = min(it.kv_end, pos + 1);                      // dead row: nothing visible
     const int n_tiles = (k_hi - k_lo + KT - 1) / KT;
 
-    // the block-table entries of the range, once, so that the loads below do not wait on them
-    const int first_page = k_lo / page;
-    const int range_pages = (k_hi + page - 1) / page - first_page;
-    for (int i = tid; i < min(range_pages, PAGE_CACHE); i += THREADS)
-        page_ids[i] = block_table[(size_t)slot * table_stride + first_page + i];
-
     pdl_wait();            // q, and the keys and values of this step's tokens, are just written
 
-    // q row into shared memory, operand layout (chunk index xor row % 8)
-    {
+    // q row into shared memory, operand layout (chunk index xor row % 8); each half four chunks
+    if (!driver) {
         const __nv_bfloat16* src = q + (size_t)(tok0 + tok) * q_stride + hq * D;
 #pragma unroll
-        for (int c = 0; c < 8; ++c)
-            cp_async16(q_s + tid * 128 + ((c ^ (tid & 7)) << 4), src + c * 8, live);
+        for (int c = 4 * half; c < 4 * half + 4; ++c)
+            cp_async16(q_s + rowi * 128 + ((c ^ (rowi & 7)) << 4), src + c * 8, live);
         asm volatile("cp.async.commit_group;\n" ::);
         asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     }
@@ -261,190 +286,244 @@ attn_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    const unsigned tmem = tmem_slot;
-    const unsigned tmem_s = tmem, tmem_o = tmem + 128;
-
-    // pages of one tile: a TMA box per page that holds keys of the range; the lanes of warp 0 take
-    // the pages in turn, lane 0 announces the bytes first
-    const int pages_per_tile = KT / page;
-    const unsigned page_bytes = (unsigned)page * 128u;
-    auto page_of = [&](int index) {
-        return index < PAGE_CACHE ? page_ids[index]
-                                  : block_table[(size_t)slot * table_stride + first_page + index];
-    };
-    auto load_tile = [&](int tile, int stage) {                  // all lanes of warp 0
-        const int kt = k_lo + tile * KT;
-        unsigned mine = 0;
-        for (int p = lane; p < pages_per_tile; p += 32) {
-            const int first = kt + p * page;
-            if (first + page <= k_lo_true || first >= k_hi) continue;
-            const int id = page_of(first / page - first_page);
-            if (id >= 0 && id < num_pages) mine += 2 * page_bytes;
-        }
-        unsigned bytes = mine;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) bytes += __shfl_xor_sync(0xffffffffu, bytes, o);
-        if (lane == 0) mbar_expect_tx(&kv_full[stage], bytes);
-        __syncwarp();
-        for (int p = lane; p < pages_per_tile; p += 32) {
-            const int first = kt + p * page;
-            if (first + page <= k_lo_true || first >= k_hi) continue;
-            const int id = page_of(first / page - first_page);
-            if (id < 0 || id >= num_pages) continue;
-            const int y = (id * kv_heads + hk) * page;
-            tma_load_2d(k_s + stage * TILE_BYTES + p * page_bytes, &map_k, &kv_full[stage], 0, y);
-            tma_load_2d(v_s + stage * TILE_BYTES + p * page_bytes, &map_v, &kv_full[stage], 0, y);
-        }
-    };
-
-    float o_row[D];
-#pragma unroll
-    for (int j = 0; j < D; ++j) o_row[j] = 0.0f;
-    float m_run = -INFINITY, l_run = 0.0f;
+    const unsigned tmem = tmem_slot;          // s buffers at columns 0 and 128, p v at 256 and 320
     const float sl = scale * 1.4426950408889634f;
-    constexpr unsigned idesc_s = instr_desc(128, 128, false);
-    constexpr unsigned idesc_o = instr_desc(128, 64, true);
     bool ok = true;
 
-    if (warp == 0) load_tile(0, 0);
-    for (int tile = 0; tile < n_tiles && ok; ++tile) {
-        const int stage = tile & 1;
-        const int kt = k_lo + tile * KT;
-        // the other stage was read by the products of tile - 1, which are complete (o_done)
-        if (warp == 0 && tile + 1 < n_tiles) load_tile(tile + 1, stage ^ 1);
-        if (tid == 0) {
-            ok = mbar_wait(&kv_full[stage], (tile >> 1) & 1, status);
+    if (warp == 9) {
+        // ------------------------------------------------------------------ copies
+        const int pages_per_tile = KT / page;
+        const unsigned page_bytes = (unsigned)page * 128u;
+        int id[4];
+        // the pages of a tile that hold keys of the range; the lanes take the pages in turn, so
+        // their block-table reads run side by side
+        auto lookup = [&](int tile) {
+            const int kt = k_lo + tile * KT;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int p = lane + 32 * i;
+                const int first = kt + p * page;
+                id[i] = -1;
+                if (p < pages_per_tile && first + page > k_lo_true && first < k_hi) {
+                    id[i] = block_table[(size_t)slot * table_stride + first / page];
+                    if (id[i] >= num_pages) id[i] = -1;
+                }
+            }
+        };
+        // a TMA box per page; lane 0 announces the bytes
+        auto issue = [&](int stage) {
+            unsigned bytes = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                if (id[i] >= 0) bytes += 2 * page_bytes;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) bytes += __shfl_xor_sync(0xffffffffu, bytes, o);
+            if (lane == 0) mbar_expect_tx(&kv_full[stage], bytes);
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if (id[i] < 0) continue;
+                const int p = lane + 32 * i;
+                const int y = (id[i] * kv_heads + hk) * page;
+                tma_load_2d(k_s + stage * TILE_BYTES + p * page_bytes, &map_k, &kv_full[stage], 0, y);
+                tma_load_2d(v_s + stage * TILE_BYTES + p * page_bytes, &map_v, &kv_full[stage], 0, y);
+            }
+        };
+        for (int t = 0; t < STAGES && t < n_tiles; ++t) {
+            lookup(t);
+            issue(t);
+        }
+        for (int tile = 0; tile + STAGES < n_tiles; ++tile) {
+            lookup(tile + STAGES);
+            // the stage is free when p v of the tile that used it is complete
+            if (ok) ok = mbar_wait(&o_done[tile & 1], (tile >> 1) & 1, status);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (lane == 0) STAMP(1, tile, 4);
+            if (ok) issue(tile % STAGES);
+            if (lane == 0) STAMP(1, tile, 5);
+        }
+    } else if (warp == 8) {
+        // ------------------------------------------------------------------ tensor core
+        constexpr unsigned idesc_s = instr_desc(128, 128, false);
+        constexpr unsigned idesc_o = instr_desc(128, 64, true);
+        // s(tile) = q k^T into s buffer tile & 1
+        auto issue_scores = [&](int tile) {
+            const int stage = tile % STAGES;
+            if (ok) ok = mbar_wait(&kv_full[stage], (tile / STAGES) & 1, status);
             if (ok) {
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 const unsigned long long a = desc_k_major(q_s);
                 const unsigned long long b = desc_k_major(k_s + stage * TILE_BYTES);
 #pragma unroll
-                for (int k = 0; k < D / 16; ++k) umma_bf16(tmem_s, a + 2 * k, b + 2 * k, idesc_s, k > 0);
+                for (int k = 0; k < D / 16; ++k)
+                    umma_bf16(tmem + 128 * (tile & 1), a + 2 * k, b + 2 * k, idesc_s, k > 0);
             }
-            umma_commit(&s_done);
-        }
-        // ---- softmax of this thread's row
-        ok = mbar_wait(&s_done, tile & 1, status);
-        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        float corr = 1.0f;
-        if (ok) {
-            const unsigned lane_addr = tmem_s + ((unsigned)(warp * 32) << 16);
-            unsigned sv[4][32];
+            umma_commit(&s_done[tile & 1]);
+        };
+        if (lane == 0) {
+            issue_scores(0);
+            if (n_tiles > 1) issue_scores(1);
+            for (int tile = 0; tile < n_tiles; ++tile) {
+                const int b = tile & 1, stage = tile % STAGES;
+                // p(tile) is written (so s(tile) has been read too) and the p v buffer is free
+                STAMP(1, tile, 0);
+                if (ok) ok = mbar_wait(&p_ready[b], (tile >> 1) & 1, status);
+                STAMP(1, tile, 1);
+                if (ok && tile >= 2) ok = mbar_wait(&o_free[b], ((tile >> 1) - 1) & 1, status);
+                if (ok) {
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                    const unsigned long long vb = desc_mn_major(v_s + stage * TILE_BYTES);
+                    const unsigned long long pa = desc_k_major(p_s + 2 * b * TILE_BYTES);
 #pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_load_32cols(lane_addr + 32 * c, sv[c]);
-            tmem_wait_loads();
-            float m_new = m_run;
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int key = kt + 32 * c + i;
-                    float s = __uint_as_float(sv[c][i]);
-                    if (key < lo || key >= hi) s = -INFINITY;
-                    sv[c][i] = __float_as_uint(s);
-                    m_new = fmaxf(m_new, s);
+                    for (int k = 0; k < KT / 16; ++k) {
+                        // 16 keys of p are 32 bytes inside a sub-tile row (the second sub-tile one
+                        // tile further); 16 keys of v are 2 groups of 8 rows = 2048 bytes
+                        umma_bf16(tmem + 256 + 64 * b,
+                                  pa + (unsigned long long)((k >> 2) * (TILE_BYTES >> 4) + 2 * (k & 3)),
+                                  vb + (unsigned long long)(k * 2048 >> 4), idesc_o, k > 0);
+                    }
                 }
-            const float m_use = m_new == -INFINITY ? 0.0f : m_new;
-            corr = fast_exp2((m_run - m_use) * sl);
-            m_run = m_new;
-            float l_add = 0.0f;
-            // p as bfloat16 into the operand layout: row tid of sub-tile (key / 64), 16-byte chunk
-            // ((key % 64) / 8) xor (tid % 8)
+                umma_commit(&o_done[b]);
+                STAMP(1, tile, 2);
+                if (tile + 2 < n_tiles) issue_scores(tile + 2);          // into the s buffer just read
+                STAMP(1, tile, 3);
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------------ softmax threads
+        float o_row[32];                                         // this half's 32 output features
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
+        for (int j = 0; j < 32; ++j) o_row[j] = 0.0f;
+        float m_run = -INFINITY, l_run = 0.0f;                   // l_run: this half's part of the sum
+        float corr_prev = 1.0f;                                  // rescale owed to the pending p v
+        const unsigned lane_bits = (unsigned)((warp & 3) * 32) << 16;
+        auto take_product = [&](int tile) {                      // o_row += p v of `tile`
+            const int b = tile & 1;
+            if (ok) ok = mbar_wait(&o_done[b], (tile >> 1) & 1, status);
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            unsigned ov[32];
+            tmem_load_32cols(tmem + 256 + 64 * b + 32 * half + lane_bits, ov);
+            tmem_wait_loads();
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            mbar_arrive(&o_free[b]);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) o_row[j] = o_row[j] * corr_prev + __uint_as_float(ov[j]);
+        };
+        for (int tile = 0; tile < n_tiles; ++tile) {
+            const int b = tile & 1, stage = tile % STAGES;
+            const int kt = k_lo + tile * KT;
+            if (tid == 0) STAMP(0, tile, 0);
+            if (ok) ok = mbar_wait(&s_done[b], (tile >> 1) & 1, status);
+            if (tid == 0) STAMP(0, tile, 1);
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            unsigned sv[2][32];
+            tmem_load_32cols(tmem + 128 * b + 64 * half + lane_bits, sv[0]);
+            tmem_load_32cols(tmem + 128 * b + 64 * half + 32 + lane_bits, sv[1]);
+            tmem_wait_loads();
+            if (tid == 0) STAMP(0, tile, 2);
+            // only the tiles at the edges of the visible range (the diagonal, a window's start,
+            // the first chunk) have keys to hide; the warp decides together
+            if (__any_sync(0xffffffffu, kt < lo || kt + KT > hi)) {
+#pragma unroll
+                for (int c = 0; c < 2; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int key = kt + 64 * half + 32 * c + i;
+                        if (key < lo || key >= hi) sv[c][i] = 0xff800000u;       // -inf
+                    }
+            }
+            float m_mine = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 2; ++c)
+#pragma unroll
+                for (int i = 0; i < 32; ++i) m_mine = fmaxf(m_mine, __uint_as_float(sv[c][i]));
+            xch[(b * 2 + half) * 128 + rowi] = m_mine;
+            asm volatile("bar.sync 1, 256;\n" ::: "memory");     // the softmax threads only
+            if (tid == 0) STAMP(0, tile, 3);
+            const float m_new = fmaxf(m_run, fmaxf(m_mine, xch[(b * 2 + (half ^ 1)) * 128 + rowi]));
+            const float m_use = m_new == -INFINITY ? 0.0f : m_new;
+            const float corr = fast_exp2((m_run - m_use) * sl);
+            m_run = m_new;
+            const float m_off = -m_use * sl;
+            float l_add = 0.0f;
+            // p as bfloat16 into the operand layout: buffer b, sub-tile `half`, row rowi, 16-byte
+            // chunk (key / 8) xor (rowi % 8).  The buffer was read by p v of tile - 2, which is
+            // complete: its result was taken in the previous iteration.
+#pragma unroll
+            for (int c = 0; c < 2; ++c)
 #pragma unroll
                 for (int i = 0; i < 32; i += 8) {
                     float p[8];
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
-                        p[j] = fast_exp2((__uint_as_float(sv[c][i + j]) - m_use) * sl);
+                        p[j] = fast_exp2(fmaf(__uint_as_float(sv[c][i + j]), sl, m_off));
                         l_add += p[j];
                     }
                     uint4 u;
                     u.x = pack2(p[0], p[1]); u.y = pack2(p[2], p[3]);
                     u.z = pack2(p[4], p[5]); u.w = pack2(p[6], p[7]);
-                    const int key_in_tile = 32 * c + i;
-                    const int sub = key_in_tile >> 6, chunk = (key_in_tile & 63) >> 3;
-                    *reinterpret_cast<uint4*>(p_s + sub * TILE_BYTES + tid * 128 +
-                                              ((chunk ^ (tid & 7)) << 4)) = u;
+                    const int chunk = (32 * c + i) >> 3;
+                    *reinterpret_cast<uint4*>(p_s + (2 * b + half) * TILE_BYTES + rowi * 128 +
+                                              ((chunk ^ (rowi & 7)) << 4)) = u;
                 }
             l_run = l_run * corr + l_add;
-        }
-        // Pages come whole: rows of v beyond the range (the rest of the last page, or keys before a
-        // window) may hold anything, and 0 * NaN is NaN in the product.  Row tid of the stage is key
-        // kt + tid: zero it when it lies outside the tile's range.
-        if (ok && (kt + tid >= k_hi || kt + tid < k_lo_true)) {
-            if (tid != 0) mbar_wait(&kv_full[stage], (tile >> 1) & 1, status);   // the pages have landed
-            uint4* vrow = reinterpret_cast<uint4*>(v_s + stage * TILE_BYTES + tid * 128);
+            if (tid == 0) STAMP(0, tile, 4);
+            // Pages come whole: rows of v beyond the range (the rest of the last page, or keys
+            // before a window) may hold anything, and 0 * NaN is NaN in the product.  Row rowi of
+            // the stage is key kt + rowi: zero it when it lies outside the tile's range.
+            if (kt + rowi >= k_hi || kt + rowi < k_lo_true) {
+                if (ok) ok = mbar_wait(&kv_full[stage], (tile / STAGES) & 1, status);
+                uint4* vrow = reinterpret_cast<uint4*>(v_s + stage * TILE_BYTES + rowi * 128) + 4 * half;
 #pragma unroll
-            for (int c = 0; c < 8; ++c) vrow[c] = make_uint4(0u, 0u, 0u, 0u);
+                for (int c = 0; c < 4; ++c) vrow[c] = make_uint4(0u, 0u, 0u, 0u);
+            }
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            mbar_arrive(&p_ready[b]);
+            if (tid == 0) STAMP(0, tile, 5);
+            // while the tensor core multiplies p v of this tile: take the previous tile's result
+            if (tile >= 1) take_product(tile - 1);
+            if (tid == 0) STAMP(0, tile, 6);
+            corr_prev = corr;
         }
-        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-        asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-        __syncthreads();
-        // ---- o_tile = p v
-        if (tid == 0) {
-            if (ok) {
-                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                const unsigned long long b = desc_mn_major(v_s + stage * TILE_BYTES);
+        take_product(n_tiles - 1);
+        pdl_trigger();
+
+        // the row's sum is the two halves' sums
+        xch[half * 128 + rowi] = l_run;
+        asm volatile("bar.sync 1, 256;\n" ::: "memory");
+        const float l_row = l_run + xch[(half ^ 1) * 128 + rowi];
+        if (ok && live) {
+            if (it.partial < 0) {
+                const float inv = l_row > 0.0f ? 1.0f / l_row : 0.0f;
+                __nv_bfloat16* o = out + (size_t)(tok0 + tok) * out_stride + hq * D + 32 * half;
 #pragma unroll
-                for (int k = 0; k < KT / 16; ++k) {
-                    // 16 keys of p are 32 bytes inside a sub-tile row; 16 keys of v are 2 groups of
-                    // 8 rows = 2048 bytes
-                    const unsigned long long a = desc_k_major(p_s + (k >> 2) * TILE_BYTES) + 2 * (k & 3);
-                    umma_bf16(tmem_o, a, b + (unsigned long long)(k * 2048 >> 4), idesc_o, k > 0);
+                for (int j = 0; j < 32; j += 8) {
+                    uint4 u;
+                    u.x = pack2(o_row[j] * inv, o_row[j + 1] * inv);
+                    u.y = pack2(o_row[j + 2] * inv, o_row[j + 3] * inv);
+                    u.z = pack2(o_row[j + 4] * inv, o_row[j + 5] * inv);
+                    u.w = pack2(o_row[j + 6] * inv, o_row[j + 7] * inv);
+                    *reinterpret_cast<uint4*>(o + j) = u;
+                }
+            } else {
+                const size_t idx = ((size_t)it.partial * kv_heads + hk) * ROWS + rowi;
+                float* pa = partial_acc + idx * D + 32 * half;
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                    *reinterpret_cast<float4*>(pa + j) =
+                        make_float4(o_row[j], o_row[j + 1], o_row[j + 2], o_row[j + 3]);
+                if (half == 0) {
+                    partial_ml[idx * 2] = m_run * scale;          // natural-log domain, as merged
+                    partial_ml[idx * 2 + 1] = l_row;
                 }
             }
-            umma_commit(&o_done);
-        }
-        const bool got = mbar_wait(&o_done, tile & 1, status);
-        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        ok = ok && got;
-        if (ok) {
-            const unsigned lane_addr = tmem_o + ((unsigned)(warp * 32) << 16);
-            unsigned ov[2][32];
-            tmem_load_32cols(lane_addr, ov[0]);
-            tmem_load_32cols(lane_addr + 32, ov[1]);
-            tmem_wait_loads();
-#pragma unroll
-            for (int j = 0; j < D; ++j)
-                o_row[j] = o_row[j] * corr + __uint_as_float(ov[j >> 5][j & 31]);
-        }
-        // the block's votes differ only after a failed wait; leave the loop together (this is also
-        // the barrier between this tile's reads of tensor memory and the next tile's products)
-        asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-        ok = __syncthreads_and(ok);
-        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    }
-    pdl_trigger();
-
-    if (ok && live) {
-        if (it.partial < 0) {
-            const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-            __nv_bfloat16* o = out + (size_t)(tok0 + tok) * out_stride + hq * D;
-#pragma unroll
-            for (int j = 0; j < D; j += 8) {
-                uint4 u;
-                u.x = pack2(o_row[j] * inv, o_row[j + 1] * inv);
-                u.y = pack2(o_row[j + 2] * inv, o_row[j + 3] * inv);
-                u.z = pack2(o_row[j + 4] * inv, o_row[j + 5] * inv);
-                u.w = pack2(o_row[j + 6] * inv, o_row[j + 7] * inv);
-                *reinterpret_cast<uint4*>(o + j) = u;
-            }
-        } else {
-            const size_t idx = ((size_t)it.partial * kv_heads + hk) * ROWS + tid;
-            float* pa = partial_acc + idx * D;
-#pragma unroll
-            for (int j = 0; j < D; j += 4)
-                *reinterpret_cast<float4*>(pa + j) =
-                    make_float4(o_row[j], o_row[j + 1], o_row[j + 2], o_row[j + 3]);
-            partial_ml[idx * 2] = m_run * scale;                  // natural-log domain, as merged
-            partial_ml[idx * 2 + 1] = l_run;
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem, TMEM_COLS);
+    if (warp == 8) tmem_dealloc(tmem, TMEM_COLS);
 }
 
 // ---------------------------------------------------------------------------------- host side
@@ -482,6 +561,11 @@ int make_page_map(CUtensorMap* map, const void* pages, long long rows, int page)
 
 }  // namespace
 
+#ifdef ATTN_TIMING
+DE_EXPORT int de_attn_tcgen05_stamps(unsigned long long* host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, attn_stamps, sizeof(attn_stamps));
+}
+#endif
 DE_EXPORT int de_attn_tcgen05_rows() { return ROWS; }
 DE_EXPORT int de_attn_tcgen05_head_dim() { return D; }
 
@@ -495,7 +579,7 @@ DE_EXPORT int de_attn_tcgen05(const void* q, int q_stride, void* out, int out_st
                               float scale, int window, int* status, void* stream) {
     if (num_items <= 0) return 0;
     if (head_dim != D || heads % kv_heads != 0) return -2;
-    if (page <= 0 || KT % page != 0 || q_stride % 8 != 0 || out_stride % 8 != 0 ||
+    if (page <= 0 || KT % page != 0 || KT / page > 128 || q_stride % 8 != 0 || out_stride % 8 != 0 ||
         ((uintptr_t)q & 15) || ((uintptr_t)out & 15) || ((uintptr_t)k_pages & 15) ||
         ((uintptr_t)v_pages & 15))
         return -3;
@@ -509,7 +593,7 @@ DE_EXPORT int de_attn_tcgen05(const void* q, int q_stride, void* out, int out_st
     cudaError_t e = cudaFuncSetAttribute(attn_tcgen05_kernel,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    dim3 grid(num_items, kv_heads);
+    dim3 grid((unsigned)num_items * (unsigned)kv_heads);
     return de_launch(attn_tcgen05_kernel, grid, dim3(THREADS), smem, (cudaStream_t)stream,
                      (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, map_k, map_v,
                      block_table, table_stride, num_pages, seq_slot, seq_qstart, seq_qlen, seq_pos0,

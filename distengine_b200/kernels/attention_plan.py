@@ -46,6 +46,16 @@ def _tiles(seq_qlen: np.ndarray, seq_pos0: np.ndarray, group: int, rows_per_tile
     return seq, row0, lo, hi
 
 
+def _longest_first(items: np.ndarray, lo: np.ndarray) -> np.ndarray:
+    """Items by falling number of keys: blocks start in this order, so the long ones of a causal
+    prompt do not start last and leave the other SMs idle at the end.  (Partial slots and combine
+    items name slots, not item indices, so the order is free.)"""
+    if len(items) < 2:
+        return items
+    keys = items[:, 3].astype(np.int64) - np.maximum(items[:, 2].astype(np.int64), lo)
+    return items[np.argsort(-keys, kind="stable")]
+
+
 def choose_chunk(num_tiles: int, kv_heads: int, longest: int) -> int:
     """The largest chunk that still gives every SM about two blocks; 0: do not split."""
     if num_tiles * kv_heads >= 2 * SM_COUNT:
@@ -70,7 +80,8 @@ def build_plan(seq_qlen: np.ndarray, seq_pos0: np.ndarray, group: int, kv_heads:
     if chunk == 0 or total == 0:
         items = np.zeros((total, 8), dtype=np.int32)
         items[:, 0], items[:, 1], items[:, 2], items[:, 3], items[:, 4] = seq, row0, 0, hi, -1
-        return AttentionPlan(items, np.zeros((0, 4), dtype=np.int32), 0, rows_per_tile, 0)
+        return AttentionPlan(_longest_first(items, lo), np.zeros((0, 4), dtype=np.int32), 0,
+                             rows_per_tile, 0)
 
     c0 = lo // chunk
     c1 = (hi - 1) // chunk
@@ -107,4 +118,5 @@ def build_plan(seq_qlen: np.ndarray, seq_pos0: np.ndarray, group: int, kv_heads:
     combine = np.zeros((len(sel), 4), dtype=np.int32)
     combine[:, 0], combine[:, 1], combine[:, 2] = seq[sel], row0[sel], part_first[sel]
     combine[:, 3] = count[sel]
-    return AttentionPlan(items, combine, int(n_part.sum()), rows_per_tile, chunk)
+    return AttentionPlan(_longest_first(items, lo[owner]), combine, int(n_part.sum()), rows_per_tile,
+                         chunk)
