@@ -1,0 +1,539 @@
+// Attention of decoded tokens in one launch per layer: every sequence of the step brings one token.
+// bfloat16 on the tensor cores (mma.sync m16n8k16, as attention_mma.cu's narrow shape: a tile of 16
+// rows, the rows being the query heads of one kv head's group, the 4 warps split the 64 keys of a
+// key tile), float32 softmax.  Compiled once per head size (-DHEAD_DIM=d).
+//
+// What is folded in, so that a layer's attention is one kernel instead of four:
+//   * rotation of q and of the token's own key (src/layers/rotary_embedding.py:45-54) and the store
+//     of that key and value into the pages (src/distengine/paged_kv_cache.py:165-167).  A block
+//     rotates its own query rows; the block whose key range holds the token's position rotates the
+//     key, stores key and value (the block of the group's first rows only) and uses them from
+//     shared memory, so nothing that this launch writes is read from the cache.  The qkv buffer is
+//     left as the product wrote it.
+//   * the merge of a split key range.  The chunks of a range are the blocks of one thread-block
+//     cluster: each leaves its unnormalised result (accumulator, maximum, sum) in its own shared
+//     memory, and after a cluster barrier every block merges a slice of the output from all
+//     blocks' shared memory (distributed shared memory), with no trip through global memory.
+//     Ranges longer than a cluster's reach take several clusters; each writes a partial result,
+//     and the cluster that finishes last (a counter per tile and kv head, left at zero again)
+//     merges them in the arithmetic of `de_attn_combine`.  No block spins on another: the cluster
+//     barrier is the hardware's, and every block of a cluster reaches both barriers on every path.
+//   * the cache rows of earlier tokens are requested before the kernel waits for the kernel before
+//     it (programmatic dependent launch): that kernel is the product that made qkv and does not
+//     touch the cache, and everything before it is complete when this one starts.
+//
+// Items (attention_plan): every tile has `cap` consecutive items (its chunks in ascending order,
+// padded with empty ones), `cap` a multiple of the cluster size; block (g, hk, rank) of the grid
+// takes item g * cluster + rank and kv head hk.
+
+#include "common.cuh"
+
+DE_DEFINE_PDL_SWITCH
+
+#include <cooperative_groups.h>
+
+#include "attention_mma_common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace {
+
+constexpr int WN = 4;                  // warps; they split the keys of a tile
+constexpr int ROWS = 16;
+constexpr int NK = KT / WN;
+constexpr int NT = NK / 8;
+constexpr int DT = D / 8;
+constexpr int CHUNKS = D / 8;          // 16-byte pieces of a key's row
+constexpr int MAX_CLUSTER = 8;
+
+// shared memory, in bytes from the start (all offsets multiples of 16)
+constexpr int OFF_K = 0;                                         // [2][KT][LDS] bf16
+constexpr int OFF_V = OFF_K + 2 * KT * LDS * 2;                  // [2][KT][LDS] bf16
+constexpr int OFF_Q = OFF_V + 2 * KT * LDS * 2;                  // [16][LDS] bf16
+constexpr int OFF_KNEW = OFF_Q + ROWS * LDS * 2;                 // [LDS] bf16
+constexpr int OFF_VNEW = OFF_KNEW + LDS * 2;                     // [LDS] bf16
+constexpr int SMEM_TILES = OFF_VNEW + LDS * 2;
+// after the key tiles are done their space is used again:
+constexpr int OFF_RED_O = 0;                                     // [WN][16][D] f32: the warps' results
+constexpr int OFF_RED_M = OFF_RED_O + WN * ROWS * D * 4;         // [WN][16] f32
+constexpr int OFF_RED_L = OFF_RED_M + WN * ROWS * 4;             // [WN][16] f32
+constexpr int OFF_BLK_O = OFF_RED_L + WN * ROWS * 4;             // [16][D] f32: the block's result,
+constexpr int OFF_BLK_M = OFF_BLK_O + ROWS * D * 4;              // [16]         read by the cluster
+constexpr int OFF_BLK_L = OFF_BLK_M + ROWS * 4;                  // [16]
+constexpr int SMEM_MERGE = OFF_BLK_L + ROWS * 4;
+constexpr int SMEM_BYTES = SMEM_TILES > SMEM_MERGE ? SMEM_TILES : SMEM_MERGE;
+static_assert(OFF_BLK_L + ROWS * 4 <= OFF_Q, "the merge area must not reach q (still in use)");
+
+__global__ void __launch_bounds__(THREADS)
+attn_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int qkv_stride,
+                   __nv_bfloat16* __restrict__ out, int out_stride,
+                   __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages,
+                   const int* __restrict__ block_table, int table_stride, int num_pages,
+                   const int* __restrict__ seq_slot, const int* __restrict__ seq_qstart,
+                   const int* __restrict__ seq_pos0, const WorkItem* __restrict__ items, int cap,
+                   float* __restrict__ partial_acc, float* __restrict__ partial_ml,
+                   int* __restrict__ counters, const float* __restrict__ inv_freq, int rot,
+                   int write_kv, int heads, int kv_heads, int page, float scale, int window,
+                   int* __restrict__ status) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(smem_raw + OFF_K);
+    __nv_bfloat16* v_s = reinterpret_cast<__nv_bfloat16*>(smem_raw + OFF_V);
+    __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw + OFF_Q);
+    __nv_bfloat16* k_new = reinterpret_cast<__nv_bfloat16*>(smem_raw + OFF_KNEW);
+    __nv_bfloat16* v_new = reinterpret_cast<__nv_bfloat16*>(smem_raw + OFF_VNEW);
+    __shared__ int s_last;
+
+    cg::cluster_group cluster = cg::this_cluster();
+    const int csize = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
+    const int group = blockIdx.x / csize;                 // (items' cluster, kv head)
+    const int hk = group % kv_heads;
+    const int item_index = (group / kv_heads) * csize + rank;
+    const WorkItem it = items[item_index];
+    const bool empty = it.kv_begin >= it.kv_end;          // padding: takes part in the merge only
+    const int g = heads / kv_heads;
+    const int pos = seq_pos0[it.seq];                     // the token's position
+    const int slot = seq_slot[it.seq], tok = seq_qstart[it.seq];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int wn = warp;
+    const int gid = lane >> 2, tig = lane & 3;
+    const int n_rows = min(ROWS, g - it.row0);
+    // the tile's clusters: `cap` items a tile, csize of them a cluster
+    const int clusters_per_tile = cap / csize;
+    const int cluster_in_tile = (item_index - it.tile * cap) / csize;
+    // the token's own key lies in this block's range and is not in the cache yet
+    const bool new_key = !empty && write_kv != 0 && pos >= it.kv_begin && pos < it.kv_end;
+
+    // every row is the same token: one key range
+    int lo = it.kv_begin;
+    if (window > 0) lo = max(lo, pos - window + 1);
+    const int hi = empty ? lo : min(it.kv_end, pos + 1);
+    const int k_lo = (lo / KT) * KT;
+
+    const size_t slab = (size_t)page * D;
+    // keys and values of a tile from the cache; the token's own row is left out (fill_new)
+    auto load_tile = [&](int kt, int stage) {
+        __nv_bfloat16* kd = k_s + stage * KT * LDS;
+        __nv_bfloat16* vd = v_s + stage * KT * LDS;
+        for (int c = threadIdx.x; c < KT * CHUNKS; c += THREADS) {
+            const int j = c / CHUNKS, ch = c - j * CHUNKS;
+            const int kpos = kt + j;
+            if (new_key && kpos == pos) continue;
+            bool ok = kpos >= lo && kpos < hi;
+            size_t off = 0;
+            if (ok) {
+                const int page_id = block_table[(size_t)slot * table_stride + kpos / page];
+                ok = page_id >= 0 && page_id < num_pages;
+                if (ok) off = ((size_t)page_id * kv_heads + hk) * slab + (size_t)(kpos % page) * D +
+                              ch * 8;
+            }
+            cp_async16(kd + j * LDS + ch * 8, k_pages + off, ok);
+            cp_async16(vd + j * LDS + ch * 8, v_pages + off, ok);
+        }
+    };
+    // the token's own key and value, from this launch and not from the cache, into their row
+    auto fill_new = [&](int kt, int stage) {
+        if (!new_key || pos < kt || pos >= kt + KT || threadIdx.x >= 2 * CHUNKS) return;
+        const int ch = threadIdx.x % CHUNKS;
+        __nv_bfloat16* dst = (threadIdx.x < CHUNKS ? k_s : v_s) + (stage * KT + pos - kt) * LDS;
+        const __nv_bfloat16* src = threadIdx.x < CHUNKS ? k_new : v_new;
+        *reinterpret_cast<uint4*>(dst + ch * 8) = *reinterpret_cast<const uint4*>(src + ch * 8);
+    };
+
+    // the first two tiles are requested before the wait (see the head of the file)
+    if (k_lo < hi) load_tile(k_lo, 0);
+    cp_async_commit();
+    if (k_lo + KT < hi) load_tile(k_lo + KT, 1);
+    cp_async_commit();
+
+    pdl_wait();                                       // qkv is the previous kernel's output
+
+    float o_acc[DT][4];
+#pragma unroll
+    for (int j = 0; j < DT; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o_acc[j][e] = 0.0f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+    const float sl = scale * 1.4426950408889634f;           // scores in the exp2 domain
+
+    if (!empty) {
+        // rotation (half-split pairs, angle = float(pos) * inv_freq[j]); features from `rot` on
+        // stay.  Every thread first requests all it needs (independent loads), then computes.
+        const __nv_bfloat16* token = qkv + (size_t)tok * qkv_stride;
+        {
+            const int half = rot / 2;
+            constexpr int TODO = (ROWS + 1) * (D / 2);            // pairs of 16 q rows and the key
+            constexpr int PER = (TODO + THREADS - 1) / THREADS;
+            __nv_bfloat16 a[PER], bb[PER];
+            float freq[PER];
+#pragma unroll
+            for (int u = 0; u < PER; ++u) {
+                const int idx = threadIdx.x + u * THREADS;
+                const int r = idx / (D / 2), j = idx - r * (D / 2);
+                const bool live = r < n_rows || (r == ROWS && new_key);
+                const int c0 = j < half ? j : rot + 2 * (j - half);
+                const int c1 = j < half ? j + half : c0 + 1;
+                const __nv_bfloat16* src =
+                    token + (size_t)(r < ROWS ? hk * g + it.row0 + r : heads + hk) * D;
+                a[u] = live ? src[c0] : __float2bfloat16_rn(0.0f);
+                bb[u] = live ? src[c1] : __float2bfloat16_rn(0.0f);
+                freq[u] = (live && j < half && inv_freq) ? inv_freq[j] : 0.0f;
+            }
+            __nv_bfloat16 vn = __float2bfloat16_rn(0.0f);
+            if (new_key && threadIdx.x < D)
+                vn = token[(size_t)(heads + kv_heads + hk) * D + threadIdx.x];
+#pragma unroll
+            for (int u = 0; u < PER; ++u) {
+                const int idx = threadIdx.x + u * THREADS;
+                const int r = idx / (D / 2), j = idx - r * (D / 2);
+                if (r > ROWS || (r == ROWS && !new_key)) continue;
+                __nv_bfloat16* dst = r < ROWS ? q_s + r * LDS : k_new;
+                const int c0 = j < half ? j : rot + 2 * (j - half);
+                const int c1 = j < half ? j + half : c0 + 1;
+                if (j < half && inv_freq && (r < n_rows || r == ROWS)) {
+                    const float angle = (float)pos * freq[u];
+                    float ra, rb;
+                    rope_rotate(__bfloat162float(a[u]), __bfloat162float(bb[u]), cosf(angle),
+                                sinf(angle), ra, rb);
+                    dst[c0] = __float2bfloat16_rn(ra);
+                    dst[c1] = __float2bfloat16_rn(rb);
+                } else {                              // unrotated features; zeros beyond the group
+                    dst[c0] = a[u];
+                    dst[c1] = bb[u];
+                }
+            }
+            if (new_key) {
+                if (threadIdx.x < D) v_new[threadIdx.x] = vn;
+                for (int j = threadIdx.x + THREADS; j < D; j += THREADS)
+                    v_new[j] = token[(size_t)(heads + kv_heads + hk) * D + j];
+            }
+        }
+        __syncthreads();
+
+        // the token's key and value into the cache: the block of the group's first rows does it
+        if (new_key && it.row0 == 0 && threadIdx.x < 2 * CHUNKS) {
+            const int page_id = block_table[(size_t)slot * table_stride + pos / page];
+            if (page_id < 0 || page_id >= num_pages) {    // a table without a page here: record, skip
+                if (threadIdx.x == 0) atomicExch(status, 1);
+            } else {
+                const size_t off =
+                    ((size_t)page_id * kv_heads + hk) * page * D + (size_t)(pos % page) * D;
+                const int ch = threadIdx.x % CHUNKS;
+                if (threadIdx.x < CHUNKS)
+                    *reinterpret_cast<uint4*>(k_pages + off + ch * 8) =
+                        *reinterpret_cast<const uint4*>(k_new + ch * 8);
+                else
+                    *reinterpret_cast<uint4*>(v_pages + off + ch * 8) =
+                        *reinterpret_cast<const uint4*>(v_new + ch * 8);
+            }
+        }
+        fill_new(k_lo, 0);
+        fill_new(k_lo + KT, 1);
+
+        unsigned qf[D / 16][4];
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const __nv_bfloat16* p = q_s + (gid + 8 * i) * LDS + kk * 16 + 2 * tig;
+                qf[kk][i] = *reinterpret_cast<const unsigned*>(p);
+                qf[kk][i + 2] = *reinterpret_cast<const unsigned*>(p + 8);
+            }
+
+        int stage = 0;
+        for (int kt = k_lo; kt < hi; kt += KT, stage ^= 1) {
+            cp_async_wait<1>();                       // this tile has landed; the next may be on its way
+            __syncthreads();
+
+            const __nv_bfloat16* kb = k_s + stage * KT * LDS + wn * NK * LDS;
+            const __nv_bfloat16* vb = v_s + stage * KT * LDS + wn * NK * LDS;
+
+            float s[NT][4];
+#pragma unroll
+            for (int j = 0; j < NT; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[j][e] = 0.0f;
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+#pragma unroll
+                for (int j = 0; j < NT; j += 2) {
+                    unsigned b[4];
+                    const int mat = lane >> 3, r = lane & 7;
+                    ldmatrix_x4(b, kb + ((j + (mat >> 1)) * 8 + r) * LDS + kk * 16 + (mat & 1) * 8);
+                    mma_bf16(s[j], qf[kk], b[0], b[1]);
+                    mma_bf16(s[j + 1], qf[kk], b[2], b[3]);
+                }
+            }
+            const int key0 = kt + wn * NK;
+            if (key0 + NK > hi || key0 < lo) {
+#pragma unroll
+                for (int j = 0; j < NT; ++j)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int key = key0 + j * 8 + 2 * tig + (e & 1);
+                        if (key < lo || key >= hi) s[j][e] = -INFINITY;
+                    }
+            }
+
+            unsigned pf[NK / 16][4];
+            {
+                float m_new[2] = {m_run[0], m_run[1]};
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    m_new[0] = fmaxf(m_new[0], fmaxf(s[j][0], s[j][1]));
+                    m_new[1] = fmaxf(m_new[1], fmaxf(s[j][2], s[j][3]));
+                }
+                float corr[2], m_use[2], l_add[2] = {0.0f, 0.0f};
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 1));
+                    m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 2));
+                    m_use[i] = m_new[i] == -INFINITY ? 0.0f : m_new[i];
+                    corr[i] = fast_exp2((m_run[i] - m_use[i]) * sl);
+                    m_run[i] = m_new[i];
+                }
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    const float p0 = fast_exp2((s[j][0] - m_use[0]) * sl);
+                    const float p1 = fast_exp2((s[j][1] - m_use[0]) * sl);
+                    const float p2 = fast_exp2((s[j][2] - m_use[1]) * sl);
+                    const float p3 = fast_exp2((s[j][3] - m_use[1]) * sl);
+                    l_add[0] += p0 + p1;
+                    l_add[1] += p2 + p3;
+                    pf[j >> 1][(j & 1) * 2] = pack_bf16(p0, p1);
+                    pf[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
+                }
+#pragma unroll
+                for (int i = 0; i < 2; ++i) l_run[i] = l_run[i] * corr[i] + l_add[i];
+#pragma unroll
+                for (int j = 0; j < DT; ++j) {
+                    o_acc[j][0] *= corr[0]; o_acc[j][1] *= corr[0];
+                    o_acc[j][2] *= corr[1]; o_acc[j][3] *= corr[1];
+                }
+            }
+#pragma unroll
+            for (int ks = 0; ks < NK / 16; ++ks) {
+#pragma unroll
+                for (int jd = 0; jd < DT; jd += 2) {
+                    unsigned b[4];
+                    const int mat = lane >> 3, r = lane & 7;
+                    ldmatrix_x4_trans(b, vb + (ks * 16 + (mat & 1) * 8 + r) * LDS +
+                                             (jd + (mat >> 1)) * 8);
+                    mma_bf16(o_acc[jd], pf[ks], b[0], b[1]);
+                    mma_bf16(o_acc[jd + 1], pf[ks], b[2], b[3]);
+                }
+            }
+            __syncthreads();                   // this stage is free: the tile after the next goes there
+            if (kt + 2 * KT < hi) {
+                load_tile(kt + 2 * KT, stage);
+                fill_new(kt + 2 * KT, stage);
+            }
+            cp_async_commit();
+        }
+    }
+    cp_async_wait<0>();
+    pdl_trigger();
+
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+    }
+
+    // ---- the block's result: the warps that split the keys, through shared memory
+    float* red_o = reinterpret_cast<float*>(smem_raw + OFF_RED_O);
+    float* red_m = reinterpret_cast<float*>(smem_raw + OFF_RED_M);
+    float* red_l = reinterpret_cast<float*>(smem_raw + OFF_RED_L);
+    float* blk_o = reinterpret_cast<float*>(smem_raw + OFF_BLK_O);
+    float* blk_m = reinterpret_cast<float*>(smem_raw + OFF_BLK_M);
+    float* blk_l = reinterpret_cast<float*>(smem_raw + OFF_BLK_L);
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int r = gid + 8 * i;
+        float* dst = red_o + ((size_t)wn * ROWS + r) * D;
+#pragma unroll
+        for (int j = 0; j < DT; ++j) {
+            dst[j * 8 + 2 * tig] = o_acc[j][2 * i];
+            dst[j * 8 + 2 * tig + 1] = o_acc[j][2 * i + 1];
+        }
+        if (tig == 0) {
+            red_m[wn * ROWS + r] = m_run[i];
+            red_l[wn * ROWS + r] = l_run[i];
+        }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < ROWS * D; e += THREADS) {
+        const int r = e / D, dd = e - r * D;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < WN; ++w) m = fmaxf(m, red_m[w * ROWS + r]);
+        float l = 0.0f, acc = 0.0f;
+#pragma unroll
+        for (int w = 0; w < WN; ++w) {
+            const float mw = red_m[w * ROWS + r];
+            if (mw == -INFINITY) continue;
+            const float f = exp2f((mw - m) * sl);
+            l += red_l[w * ROWS + r] * f;
+            acc += red_o[((size_t)w * ROWS + r) * D + dd] * f;
+        }
+        blk_o[r * D + dd] = acc;
+        if (dd == 0) {
+            blk_m[r] = m;                                      // exp2 domain (times sl)
+            blk_l[r] = l;
+        }
+    }
+
+    // ---- the cluster's result: every block merges a slice of (row, feature) from all blocks
+    cluster.sync();
+    const int total = n_rows * D;
+    const int slice = (total + csize - 1) / csize;
+    const int e_end = min(total, (rank + 1) * slice);
+    const bool final_here = clusters_per_tile == 1;
+    const size_t part_slot = (size_t)it.tile * clusters_per_tile + cluster_in_tile;
+    __nv_bfloat16* out_token = out + (size_t)tok * out_stride + (size_t)(hk * g + it.row0) * D;
+    for (int e = rank * slice + threadIdx.x; e < e_end; e += THREADS) {
+        const int r = e / D, dd = e - r * D;
+        float mc[MAX_CLUSTER], lc[MAX_CLUSTER], ac[MAX_CLUSTER];
+#pragma unroll
+        for (int c = 0; c < MAX_CLUSTER; ++c) {               // independent remote loads
+            mc[c] = -INFINITY; lc[c] = 0.0f; ac[c] = 0.0f;
+            if (c < csize) {
+                mc[c] = cluster.map_shared_rank(blk_m, c)[r];
+                lc[c] = cluster.map_shared_rank(blk_l, c)[r];
+                ac[c] = cluster.map_shared_rank(blk_o, c)[r * D + dd];
+            }
+        }
+        float m = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < MAX_CLUSTER; ++c) m = fmaxf(m, mc[c]);
+        float l = 0.0f, acc = 0.0f;
+#pragma unroll
+        for (int c = 0; c < MAX_CLUSTER; ++c) {
+            if (mc[c] == -INFINITY) continue;                 // no visible key there (or no block)
+            const float f = exp2f((mc[c] - m) * sl);
+            l += lc[c] * f;
+            acc = fmaf(ac[c], f, acc);
+        }
+        if (final_here) {
+            out_token[r * D + dd] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+        } else {
+            const size_t idx = (part_slot * kv_heads + hk) * ROWS + r;
+            partial_acc[idx * D + dd] = acc;
+            if (dd == 0) {
+                partial_ml[idx * 2] = m * scale;              // natural-log domain, as merged
+                partial_ml[idx * 2 + 1] = l;
+            }
+        }
+    }
+    if (!final_here) __threadfence();
+    cluster.sync();                    // nobody leaves while its shared memory may still be read
+    if (final_here || rank != 0) return;
+
+    // ---- several clusters a tile: the one that finishes last merges their partial results, in
+    // ascending order of the chunks.  Clusters of padding only do not count and are not counted on.
+    const int live_clusters = (it.chunks + csize - 1) / csize;
+    if (cluster_in_tile >= live_clusters) return;
+    if (threadIdx.x == 0) {
+        __threadfence();
+        int* counter = counters + (size_t)it.tile * kv_heads + hk;
+        const int before = atomicAdd(counter, 1);
+        s_last = before == live_clusters - 1;
+        if (s_last) *counter = 0;                    // as the next launch expects it
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const size_t step = (size_t)kv_heads * ROWS;                   // from one slot to the next
+    const size_t row0_idx = ((size_t)it.tile * clusters_per_tile * kv_heads + hk) * ROWS;
+    for (int e = threadIdx.x; e < total; e += THREADS) {
+        const int r = e / D, dd = e - r * D;
+        const size_t idx0 = row0_idx + r;
+        float m = -INFINITY;
+        for (int c0 = 0; c0 < live_clusters; c0 += 4) {
+            float mm[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                mm[u] = c0 + u < live_clusters ? __ldcg(partial_ml + (idx0 + (c0 + u) * step) * 2)
+                                               : -INFINITY;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) m = fmaxf(m, mm[u]);
+        }
+        float l = 0.0f, acc = 0.0f;
+        for (int c0 = 0; c0 < live_clusters; c0 += 4) {
+            float2 ml[4];
+            float pa[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {              // independent loads: four chunks in flight
+                const bool have = c0 + u < live_clusters;
+                const size_t idx = idx0 + (c0 + u) * step;
+                ml[u] = have ? __ldcg(reinterpret_cast<const float2*>(partial_ml) + idx)
+                             : make_float2(-INFINITY, 0.0f);
+                pa[u] = have ? __ldcg(partial_acc + idx * D + dd) : 0.0f;
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (ml[u].x == -INFINITY) continue;   // the chunk held no visible key
+                const float f = expf(ml[u].x - m);
+                l += ml[u].y * f;
+                acc = fmaf(pa[u], f, acc);
+            }
+        }
+        const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+        out_token[r * D + dd] = __float2bfloat16_rn(acc * inv);
+    }
+}
+
+}  // namespace
+
+DE_EXPORT int de_attn_decode_head_dim() { return D; }
+DE_EXPORT int de_attn_decode_max_cluster() { return MAX_CLUSTER; }
+
+// `items`: tiles x `cap` work items (see the head of the file), `cluster` blocks a cluster (1, 2, 4
+// or 8; `cap` a multiple of it).  `partial_acc` / `partial_ml`: room for tiles * cap / cluster
+// partial results (each kv_heads x 16 rows), used when cap > cluster.  `counters`: int32, one per
+// (tile, kv head), zero before the first launch.  `inv_freq` null: no rotation.  `write_kv` 0: the
+// layer reads a cache that an earlier layer of the step wrote, the token's key included.
+DE_EXPORT int de_attn_decode(const void* qkv, int qkv_stride, void* out, int out_stride,
+                             void* k_pages, void* v_pages, const int* block_table,
+                             int table_stride, int num_pages, const int* seq_slot,
+                             const int* seq_qstart, const int* seq_pos0, const int* items,
+                             int num_items, int cap, int cluster, float* partial_acc,
+                             float* partial_ml, int* counters, const float* inv_freq, int rot,
+                             int write_kv, int heads, int kv_heads, int head_dim, int page,
+                             float scale, int window, int* status, void* stream) {
+    if (num_items <= 0) return 0;
+    if (head_dim != D || heads % kv_heads != 0) return -2;
+    if (rot < 0 || rot > D || (rot & 1)) return -2;
+    if (cluster < 1 || cluster > MAX_CLUSTER || (cluster & (cluster - 1)) || cap < cluster ||
+        cap % cluster != 0 || num_items % cap != 0)
+        return -4;
+    if (cap > cluster && (partial_acc == nullptr || partial_ml == nullptr)) return -4;
+    // 16-byte rows of keys and values
+    if (qkv_stride % 8 != 0 || out_stride % 2 != 0 || ((uintptr_t)qkv & 15) ||
+        ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15))
+        return -3;
+    if (SMEM_BYTES > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) return (int)e;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)num_items * (unsigned)kv_heads);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)cluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_pdl ? 2 : 1;
+    return de_check(cudaLaunchKernelEx(
+        &cfg, attn_decode_kernel, (const __nv_bfloat16*)qkv, qkv_stride, (__nv_bfloat16*)out,
+        out_stride, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, block_table, table_stride,
+        num_pages, seq_slot, seq_qstart, seq_pos0, (const WorkItem*)items, cap, partial_acc,
+        partial_ml, counters, inv_freq, rot, write_kv, heads, kv_heads, page, scale, window, status));
+}

@@ -72,6 +72,15 @@ __device__ __forceinline__ void pdl_trigger() {
 }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 
+// One rotated pair of features (a, b) by the angle whose cosine and sine are (c, s).  The products
+// and their sum are rounded one by one (no fused multiply-add), so that every kernel that rotates
+// gives the same bits and a plain float32 implementation can be matched exactly.
+__device__ __forceinline__ void rope_rotate(float a, float b, float c, float s, float& ra,
+                                            float& rb) {
+    ra = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
+    rb = __fadd_rn(__fmul_rn(b, c), __fmul_rn(a, s));
+}
+
 static int g_pdl = 1;          // per library; de_set_pdl switches it
 
 template <typename... KArgs, typename... Args>

@@ -254,8 +254,10 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride,
         for (int h = threadIdx.y; h < heads + kv_heads; h += blockDim.y) {
             T* x = row + (size_t)h * d;
             const float a = to_float(x[j]), b = to_float(x[j + half]);
-            const T ra = from_float<T>(a * c - b * s);
-            const T rb = from_float<T>(b * c + a * s);
+            float fa, fb;
+            rope_rotate(a, b, c, s, fa, fb);
+            const T ra = from_float<T>(fa);
+            const T rb = from_float<T>(fb);
             if (h < heads) {
                 x[j] = ra;
                 x[j + half] = rb;

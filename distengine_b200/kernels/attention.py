@@ -22,7 +22,7 @@ import torch
 import os
 
 from . import library
-from .attention_plan import build_plan, choose_chunk
+from .attention_plan import build_plan, choose_chunk, choose_decode_split
 from .ops import _check, _i32, _need, _ptr, _stream, _tag
 
 MAX_HEAD_DIM = 256
@@ -64,6 +64,7 @@ class AttentionLauncher:
             self.shapes = [_Shape("wide", 128 if head_dim <= 64 else 64, 0),
                            _Shape("narrow", NARROW_ROWS, 1)]
             self.module = ("attention_mma", (f"HEAD_DIM={head_dim}",))
+            self.decode_module = ("attention_decode", (f"HEAD_DIM={head_dim}",))
             # prompt portions at head size 64: the tcgen05 kernel (tensor-memory accumulators, TMA
             # page loads) takes the wide tiles; DISTENGINE_B200_ATTENTION=mma keeps the mma.sync one
             if head_dim == 64 and os.environ.get("DISTENGINE_B200_ATTENTION", "tcgen05") != "mma":
@@ -71,12 +72,19 @@ class AttentionLauncher:
         else:
             self.shapes = [_Shape("rows8", 8, -1)]
             self.module = ("attention_simt", ())
+        # steps of decoded tokens only: rotation, cache write, attention and merge in one launch;
+        # DISTENGINE_B200_DECODE_ATTENTION=split keeps them apart
+        self.fused_decode = (self.tensor_cores and os.environ.get(
+            "DISTENGINE_B200_DECODE_ATTENTION", "fused") != "split")
         self.key = (f"attention/{'mma' if self.tensor_cores else 'simt'}/{self.group}/"
                     f"{kv_heads}/{head_dim}/{self.window}")
 
     def modules(self) -> list[tuple[str, tuple[str, ...]]]:
         """The kernel libraries this launcher calls (to compile them side by side up front)."""
-        return [self.module, ("attention_simt", ())]
+        extra = [self.decode_module] if self.fused_decode else []
+        if any(shape.code == 2 for shape in self.shapes):
+            extra.append(("attention_tcgen05", ()))
+        return [self.module, ("attention_simt", ())] + extra
 
     # ------------------------------------------------------------------ host side
     def _split(self, seq_qlen: np.ndarray) -> list[np.ndarray]:
@@ -90,14 +98,45 @@ class AttentionLauncher:
         return [np.where(narrow, 0, seq_qlen).astype(np.int32),
                 np.where(narrow, seq_qlen, 0).astype(np.int32)]
 
+    def _prepare_decode(self, prep, force_split: "tuple[int, int, int] | None") -> None:
+        """A step in which every sequence brings one token: the work list of the one-launch
+        decode kernel (``csrc/attention_decode.cu``)."""
+        host = prep.host
+        rows = NARROW_ROWS
+        tiles = len(host.seq_qlen) * ((self.group + rows - 1) // rows)
+        if prep.graph_shape is not None:
+            span = int(prep.graph_shape["context_cap"])
+        else:
+            span = int(host.seq_pos0.max()) + 1
+        if self.window:
+            span = min(span, self.window)
+        cluster, clusters, chunk = force_split or choose_decode_split(tiles, self.kv_heads, span)
+        # chunks lie at absolute multiples of `chunk`: a window that starts inside one reaches
+        # into one chunk more
+        cap = clusters * cluster
+        if self.window and force_split is None:
+            need = (span + chunk - 1) // chunk + 1
+            cap = (need + cluster - 1) // cluster * cluster
+        plan = build_plan(host.seq_qlen, host.seq_pos0, self.group, self.kv_heads, rows,
+                          self.window, chunk, cap, sort=False)
+        prep.add(f"{self.key}/decode/items", plan.items)
+        prep.notes[self.key] = ()
+        prep.notes[self.key + "/decode"] = (tiles, cluster, cap)
+
     def prepare(self, prep, force_chunk: "int | None" = None,
-                force_cap: "int | None" = None, force_shape: "str | None" = None) -> None:
+                force_cap: "int | None" = None, force_shape: "str | None" = None,
+                force_split: "tuple[int, int, int] | None" = None) -> None:
         """Add this step's work lists to ``prep`` (once per step for all layers of this shape).
         The ``force_*`` arguments pin the chunk size, the chunk cap and the tile shape; tests use
         them to reach every path at small sizes."""
         if self.key in prep.notes:
             return
         host = prep.host
+        one_each = bool(len(host.seq_qlen)) and bool((host.seq_qlen == 1).all())
+        if self.fused_decode and one_each and force_shape is None:
+            self._prepare_decode(prep, force_split)
+            return
+        prep.notes[self.key + "/decode"] = None
         notes = {}
         parts = self._split(host.seq_qlen)
         if force_shape is not None:
@@ -164,6 +203,54 @@ class AttentionLauncher:
                          ctx.seq_slot, ctx.seq_qstart, ctx.seq_qlen, ctx.seq_pos0, items, combine,
                          shape.rows, acc, ml, self.heads, self.kv_heads, d, self.scale, self.window,
                          getattr(ctx, "status", None))
+
+
+    def decode_step(self, ctx) -> bool:
+        """Whether ``run_decode`` takes this step (it then also rotates and stores k and v)."""
+        return ctx.notes.get(self.key + "/decode") is not None
+
+    def run_decode(self, qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor,
+                   v_pages: torch.Tensor, block_table: torch.Tensor,
+                   inv_freq: "torch.Tensor | None", rotary_dim: int, writes: bool, ctx) -> None:
+        """A step of decoded tokens in one launch.  ``qkv``: rows [q heads | k heads | v heads]
+        as the product left them; q and k are rotated inside, k and v stored in the pages
+        (``writes``), the chunks of a split key range merged inside the kernel."""
+        d = self.head_dim
+        _need(qkv.stride(1) == 1 and out.stride(1) == 1 and qkv.dtype == out.dtype
+              == k_pages.dtype == self.dtype and qkv.shape[1] == (self.heads + 2 * self.kv_heads) * d,
+              "decode attention: qkv, out and the pages must have the layer's dtype, and qkv rows "
+              "hold q, k and v")
+        _need(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dim() == 4
+              and k_pages.shape[1] == self.kv_heads and k_pages.shape[3] == d
+              and v_pages.shape == k_pages.shape,
+              "decode attention: pages must be [pages, kv_heads, page, head_dim]")
+        _i32(block_table, "block_table")
+        items = ctx.arrays[f"{self.key}/decode/items"]
+        for name, t in (("seq_slot", ctx.seq_slot), ("seq_qstart", ctx.seq_qstart),
+                        ("seq_pos0", ctx.seq_pos0), ("items", items)):
+            _i32(t, name)
+        tiles, cluster, cap = ctx.notes[self.key + "/decode"]
+        _need(items.shape[0] == tiles * cap, "decode attention: the plan's size")
+        acc = ml = None
+        if cap > cluster:                         # several clusters a tile: partial results
+            rows = tiles * (cap // cluster) * self.kv_heads * NARROW_ROWS
+            acc = ctx.buffer("attention.partial_acc.decode", (rows * d,), torch.float32)
+            ml = ctx.buffer("attention.partial_ml.decode", (rows * 2,), torch.float32)
+        counters = ctx.buffer("attention.counters", (max(tiles, 1) * self.kv_heads,), torch.int32,
+                              zero=True)
+        if inv_freq is not None:
+            _need(inv_freq.dtype == torch.float32 and inv_freq.is_contiguous()
+                  and inv_freq.shape[0] * 2 == rotary_dim, "decode attention: inv_freq must be "
+                  "float32 [rotary_dim / 2]")
+        lib = library.load(*self.decode_module)
+        _check(lib.de_attn_decode(
+            qkv.data_ptr(), qkv.stride(0), out.data_ptr(), out.stride(0), k_pages.data_ptr(),
+            v_pages.data_ptr(), block_table.data_ptr(), block_table.stride(0), k_pages.shape[0],
+            ctx.seq_slot.data_ptr(), ctx.seq_qstart.data_ptr(), ctx.seq_pos0.data_ptr(),
+            items.data_ptr(), items.shape[0], cap, cluster, _ptr(acc), _ptr(ml),
+            counters.data_ptr(), _ptr(inv_freq), int(rotary_dim) if inv_freq is not None else 0,
+            1 if writes else 0, self.heads, self.kv_heads, d, k_pages.shape[2],
+            float(self.scale), self.window, ctx.status.data_ptr(), _stream()), "decode attention")
 
 
 def launch_items(code: int, module, q, out, k_pages, v_pages, block_table, seq_slot, seq_qstart,

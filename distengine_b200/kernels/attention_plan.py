@@ -5,7 +5,9 @@ head's group), token-major) together with a range of key positions.  Prompt port
 per tile, covering all keys up to the tile's last position.  When a step has too few tiles to fill
 the GPU (decoded tokens over long contexts), a tile's key range is cut into chunks at absolute
 multiples of ``chunk``; each chunk writes a partial result and a combine item names the chunks of
-the tile.  The layout of an item matches ``struct WorkItem`` / ``CombineItem`` in the kernels.
+the tile.  An item is (seq, row0, kv_begin, kv_end, partial slot or -1, the tile's first partial slot,
+the tile's number of chunks that hold keys, the tile's index): ``struct WorkItem`` in the kernels;
+a combine item is ``CombineItem``.
 """
 
 from __future__ import annotations
@@ -66,12 +68,36 @@ def choose_chunk(num_tiles: int, kv_heads: int, longest: int) -> int:
     return CHUNKS[-1]
 
 
+def choose_decode_split(num_tiles: int, kv_heads: int, span: int,
+                        max_cluster: int = 8) -> tuple[int, int, int]:
+    """How the one-launch decode kernel cuts key ranges of up to ``span`` keys:
+    (blocks a cluster, clusters a tile, chunk length).  The chunks of a cluster merge through
+    shared memory; several clusters a tile merge through global memory, which costs a few
+    microseconds, so a tile gets more than one cluster only when ranges are long and the step
+    would otherwise leave most of the GPU idle."""
+    blocks = max(num_tiles * kv_heads, 1)
+    tiles_of_keys = max((span + 63) // 64, 1)
+    cluster = 1
+    # about four blocks an SM at most, and no block without a whole tile of 64 keys
+    while (cluster < max_cluster and blocks * cluster * 2 <= 4 * SM_COUNT
+           and cluster * 2 <= tiles_of_keys):
+        cluster *= 2
+    clusters = (span + cluster * 2048 - 1) // (cluster * 2048)          # 2048 keys a block at most
+    while (blocks * cluster * clusters < 2 * SM_COUNT
+           and span >= cluster * (clusters + 1) * 256):                   # 256 keys a block at least
+        clusters += 1
+    per_block = (span + cluster * clusters - 1) // (cluster * clusters)
+    chunk = max((per_block + 63) // 64 * 64, 64)
+    return cluster, clusters, chunk
+
+
 def build_plan(seq_qlen: np.ndarray, seq_pos0: np.ndarray, group: int, kv_heads: int,
                rows_per_tile: int, window: int = 0, chunk: "int | None" = None,
-               chunks_cap: "int | None" = None) -> AttentionPlan:
+               chunks_cap: "int | None" = None, sort: bool = True) -> AttentionPlan:
     """``chunk`` None: chosen from the step's shape.  ``chunks_cap`` (with a given chunk): every
     tile gets exactly that many items and one combine item, padded with empty ones, so that the
-    arrays' shapes depend on the number of tiles only (what a replayed CUDA graph needs)."""
+    arrays' shapes depend on the number of tiles only (what a replayed CUDA graph needs).
+    ``sort`` false keeps the items in the order of the tiles and their chunks."""
     seq, row0, lo, hi = _tiles(seq_qlen, seq_pos0, group, rows_per_tile, window)
     total = len(seq)
     if chunk is None:
@@ -80,8 +106,9 @@ def build_plan(seq_qlen: np.ndarray, seq_pos0: np.ndarray, group: int, kv_heads:
     if chunk == 0 or total == 0:
         items = np.zeros((total, 8), dtype=np.int32)
         items[:, 0], items[:, 1], items[:, 2], items[:, 3], items[:, 4] = seq, row0, 0, hi, -1
-        return AttentionPlan(_longest_first(items, lo), np.zeros((0, 4), dtype=np.int32), 0,
-                             rows_per_tile, 0)
+        items[:, 6], items[:, 7] = 1, np.arange(total)
+        return AttentionPlan(_longest_first(items, lo) if sort else items,
+                             np.zeros((0, 4), dtype=np.int32), 0, rows_per_tile, 0)
 
     c0 = lo // chunk
     c1 = (hi - 1) // chunk
@@ -114,9 +141,12 @@ def build_plan(seq_qlen: np.ndarray, seq_pos0: np.ndarray, group: int, kv_heads:
     items = np.zeros((num_items, 8), dtype=np.int32)
     items[:, 0], items[:, 1], items[:, 2], items[:, 3], items[:, 4] = (
         seq[owner], row0[owner], begin, end, partial)
+    # the tile of an item: its first partial slot, how many of its items hold keys, its index
+    items[:, 5], items[:, 6], items[:, 7] = part_first[owner], count[owner], owner
     sel = np.nonzero(split)[0]
     combine = np.zeros((len(sel), 4), dtype=np.int32)
     combine[:, 0], combine[:, 1], combine[:, 2] = seq[sel], row0[sel], part_first[sel]
     combine[:, 3] = count[sel]
-    return AttentionPlan(_longest_first(items, lo[owner]), combine, int(n_part.sum()), rows_per_tile,
-                         chunk)
+    if sort:
+        items = _longest_first(items, lo[owner])
+    return AttentionPlan(items, combine, int(n_part.sum()), rows_per_tile, chunk)

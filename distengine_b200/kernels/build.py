@@ -35,6 +35,7 @@ MODULES: dict[str, tuple[str, tuple[str, ...]]] = {
     "linear_small": ("linear_small.cu", ()),
     "gemm_tcgen05": ("gemm_tcgen05.cu", ()),
     "attention_mma": ("attention_mma.cu", ()),          # built per head size: HEAD_DIM=<d>
+    "attention_decode": ("attention_decode.cu", ()),    # built per head size: HEAD_DIM=<d>
     "attention_tcgen05": ("attention_tcgen05.cu", ()),  # head size 64
     "decode_fused": ("decode_fused.cu", ()),            # built per head size: HEAD_DIM=<d>
 }
@@ -69,7 +70,9 @@ def _build_dir() -> str:
 
 def _digest(source: str, defines: tuple[str, ...], libs: tuple[str, ...]) -> str:
     h = hashlib.sha256()
-    for path in (os.path.join(CSRC, source), os.path.join(CSRC, "common.cuh")):
+    # the source and every header beside it (a change of a shared header rebuilds all modules)
+    headers = sorted(name for name in os.listdir(CSRC) if name.endswith((".cuh", ".h")))
+    for path in [os.path.join(CSRC, source)] + [os.path.join(CSRC, name) for name in headers]:
         with open(path, "rb") as handle:
             h.update(handle.read())
     h.update(repr((NVCC_FLAGS, defines, libs)).encode())

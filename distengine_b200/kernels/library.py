@@ -57,6 +57,11 @@ SIGNATURES: dict[str, dict[str, list]] = {
         "de_attn_mma_head_dim": [], "de_attn_mma_rows": [I],
         "de_attn_mma": [I, P, I, P, I, P, P, P, I, I, P, P, P, P, P, I, P, P, I, I, I, I, F, I, P],
     },
+    "attention_decode": {
+        "de_attn_decode_head_dim": [], "de_attn_decode_max_cluster": [],
+        "de_attn_decode": [P, I, P, I, P, P, P, I, I, P, P, P, P, I, I, I, P, P, P, P, I, I, I, I,
+                           I, I, F, I, P, P],
+    },
 }
 
 _loaded: dict[tuple[str, tuple[str, ...]], ctypes.CDLL] = {}
@@ -65,8 +70,10 @@ _loaded: dict[tuple[str, tuple[str, ...]], ctypes.CDLL] = {}
 def default_build_requests() -> list[tuple[str, tuple[str, ...]]]:
     """Every module; the per-head-size attention for the head sizes of common models."""
     requests = [(module, ()) for module in _build.MODULES
-                if module in SIGNATURES and module not in ("attention_mma", "decode_fused")]  # noqa
+                if module in SIGNATURES
+                and module not in ("attention_mma", "attention_decode", "decode_fused")]
     return (requests + [("attention_mma", (f"HEAD_DIM={d}",)) for d in (64, 128)]
+            + [("attention_decode", (f"HEAD_DIM={d}",)) for d in (64, 128)]
             + [("decode_fused", (f"HEAD_DIM={d}",)) for d in (64, 128)])
 
 

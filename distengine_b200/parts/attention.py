@@ -73,11 +73,16 @@ class PagedAttention(Mixer):
                             qkv[:, self.heads * d: (self.heads + self.kv_heads) * d]
                             .view(n, self.kv_heads, d), ctx)
         inv_freq, rotary_dim = self.position.rotation_table()
-        ops.rope_kv_write(qkv, ctx.positions, ctx.token_slot, inv_freq, rotary_dim, self.heads,
-                          self.kv_heads, d, cache.k_pages, cache.v_pages, cache.block_table,
-                          cache.writes, ctx.status)
         out = ctx.buffer("attention.context", (n, self.heads * d))
-        self.kernels.run(qkv, out, cache.k_pages, cache.v_pages, cache.block_table, ctx)
+        if self.kernels.decode_step(ctx):
+            # decoded tokens only: rotation, cache write, attention and merge are one kernel
+            self.kernels.run_decode(qkv, out, cache.k_pages, cache.v_pages, cache.block_table,
+                                    inv_freq, rotary_dim, cache.writes, ctx)
+        else:
+            ops.rope_kv_write(qkv, ctx.positions, ctx.token_slot, inv_freq, rotary_dim,
+                              self.heads, self.kv_heads, d, cache.k_pages, cache.v_pages,
+                              cache.block_table, cache.writes, ctx.status)
+            self.kernels.run(qkv, out, cache.k_pages, cache.v_pages, cache.block_table, ctx)
         branch = ctx.buffer("attention.out", (n, self.width))
         ops.linear(out, self.w_o, out=branch)
         return branch

@@ -31,14 +31,18 @@ class Workspace:
         self._buffers: dict[str, torch.Tensor] = {}
         self.generation = 0          # grows whenever a buffer moves: captured graphs are stale then
 
-    def get(self, name: str, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+    def get(self, name: str, shape: tuple[int, ...], dtype: torch.dtype,
+            zero: bool = False) -> torch.Tensor:
+        """``zero``: the buffer is zero when it is made (or made anew, larger); its users leave it
+        zero after every use (counters that a kernel resets itself)."""
         count = 1
         for s in shape:
             count *= int(s)
         buf = self._buffers.get(name)
         if buf is None or buf.dtype != dtype or buf.numel() < count:
             grow = count if buf is None or buf.dtype != dtype else max(count, 2 * buf.numel())
-            buf = torch.empty(max(grow, 1), dtype=dtype, device=self.device)
+            make = torch.zeros if zero else torch.empty
+            buf = make(max(grow, 1), dtype=dtype, device=self.device)
             self._buffers[name] = buf
             self.generation += 1
         return buf[:count].view(shape)
@@ -104,9 +108,9 @@ class StepContext:
     status: torch.Tensor                         # int32 [1]; a kernel sets it when it skips work
     extras: dict[str, Any] = field(default_factory=dict)
 
-    def buffer(self, name: str, shape: tuple[int, ...],
-               dtype: "torch.dtype | None" = None) -> torch.Tensor:
-        return self.workspace.get(name, shape, dtype or self.dtype)
+    def buffer(self, name: str, shape: tuple[int, ...], dtype: "torch.dtype | None" = None,
+               zero: bool = False) -> torch.Tensor:
+        return self.workspace.get(name, shape, dtype or self.dtype, zero)
 
 
 class ResidualStream:

@@ -115,6 +115,45 @@ def run_paged_attention(fx: PagedFixture, q_list, heads, kv_heads, head_dim, sca
     return out.float().cpu(), dict(prep.notes[launcher.key])
 
 
+def run_decode_attention(fx: PagedFixture, qkv, heads, kv_heads, head_dim, scale, window, inv_freq,
+                         rotary_dim, writes, split=None, repeats=1):
+    """One decoded token per sequence of ``fx`` (at its last position) through the launcher's
+    one-kernel decode path.  ``qkv`` [sequences, (heads + 2 kv_heads) * d]: unrotated q, k, v of
+    the tokens.  ``split``: (blocks a cluster, clusters a tile, chunk length) or None for the
+    launcher's choice.  Returns the output (float32, CPU) and the pages afterwards (float32, CPU)."""
+    from types import SimpleNamespace
+    from distengine_b200.kernels.attention import AttentionLauncher
+    from distengine_b200.parts.context import StepPrep, Workspace
+    dev, dtype = fx.device, fx.dtype
+    n = len(fx.kv_lens)
+    qlen = np.ones(n, dtype=np.int32)
+    pos0 = np.array([length - 1 for length in fx.kv_lens], dtype=np.int32)
+    qstart = np.arange(n, dtype=np.int32)
+    launcher = AttentionLauncher(dtype, heads, kv_heads, head_dim, scale, window)
+    prep = StepPrep(SimpleNamespace(seq_qlen=qlen, seq_pos0=pos0))
+    launcher.prepare(prep, force_split=split)
+    k_pages, v_pages, table = fx.to_device()
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(dev)
+    workspace = Workspace(torch.device(dev))
+    ctx = SimpleNamespace(seq_slot=t(np.array(fx.slots)), seq_qstart=t(qstart), seq_qlen=t(qlen),
+                          seq_pos0=t(pos0), notes=prep.notes,
+                          arrays={k: t(v) for k, v in prep.extra.items()},
+                          status=torch.zeros(1, dtype=torch.int32, device=dev),
+                          buffer=lambda name, shape, dt=None, zero=False: workspace.get(
+                              name, shape, dt or dtype, zero))
+    assert launcher.decode_step(ctx), "a step of single tokens must take the decode kernel"
+    dev_qkv = qkv.to(dev, dtype)
+    before = dev_qkv.clone()
+    for _ in range(repeats):        # again on the same buffers: counters must be left at zero
+        out = torch.full((n, heads * head_dim), float("nan"), dtype=dtype, device=dev)
+        launcher.run_decode(dev_qkv, out, k_pages, v_pages, table,
+                            None if inv_freq is None else inv_freq.to(dev), rotary_dim, writes, ctx)
+    torch.cuda.synchronize()
+    assert ctx.status.item() == 0
+    assert torch.equal(dev_qkv, before), "the decode kernel must leave qkv as it was"
+    return out.float().cpu(), k_pages.float().cpu(), v_pages.float().cpu()
+
+
 class PartHarness:
     """Runs single parts through the engine's own step machinery (``StepRunner`` and
     ``CacheManager``): ``run(entries, fn)`` calls ``fn(ctx, bindings)`` with the step's context."""

@@ -323,6 +323,65 @@ def test_paged_attention_one_far_key_stands_out(dtype, far):
             assert_close(got, want, dtype, f"far key {far} chunk={chunk} {shape}")
 
 
+@pytest.mark.parametrize("writes", [True, False])
+@pytest.mark.parametrize("heads,kv_heads,d,page,rot,window",
+                         [(8, 2, 64, 16, 64, None), (6, 1, 48, 32, 24, None),
+                          (32, 4, 64, 16, 64, None), (16, 2, 128, 64, 128, 100),
+                          (40, 2, 32, 8, 32, None), (4, 4, 16, 16, 0, None),
+                          (3, 1, 80, 4, 80, 7)])
+def test_decode_attention_in_one_launch(heads, kv_heads, d, page, rot, window, writes):
+    """Decoded tokens: rotation of q and k, the cache write, attention and the merge of split key
+    ranges in one kernel.  The token's own key is not in the cache beforehand (NaN stands there),
+    so it must come from the launch itself; with ``writes`` off it is there and must be left."""
+    from gpu_helpers import run_decode_attention
+    dtype, theta = torch.bfloat16, 10000.0
+    g = torch.Generator().manual_seed(heads * d + page)
+    kv_lens = [130, 1, 77, 300, 1101, 64, 65]
+    n = len(kv_lens)
+    fx = PagedFixture(kv_lens, kv_heads, d, page, dtype, DEV, seed=d + page)
+    qkv = torch.randn(n, (heads + 2 * kv_heads) * d, generator=g).to(dtype)
+    x = qkv.float().view(n, heads + 2 * kv_heads, d)
+    positions = torch.tensor([length - 1 for length in kv_lens], dtype=torch.int32)
+    q, k_new = x[:, :heads].clone(), x[:, heads: heads + kv_heads].clone()
+    inv_freq = None
+    if rot:
+        inv_freq = 1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))
+        q[..., :rot] = plain.plain_rope(q[..., :rot], positions, theta, dtype)
+        k_new[..., :rot] = plain.plain_rope(k_new[..., :rot], positions, theta, dtype)
+    v_new = x[:, heads + kv_heads:]
+    for i in range(n):
+        fx.k[i][-1], fx.v[i][-1] = k_new[i], v_new[i]
+    want = _plain_attention_case(fx, [q[i: i + 1] for i in range(n)], heads, kv_heads, d,
+                                 d ** -0.5, window, dtype)
+    fx.rewrite()
+    pages_full = fx.k_pages.clone(), fx.v_pages.clone()
+    if writes:                                # the cache does not hold the tokens' own keys yet
+        for i, length in enumerate(kv_lens):
+            pid = int(fx.block_table[fx.slots[i], (length - 1) // page])
+            fx.k_pages[pid, :, (length - 1) % page] = float("nan")
+            fx.v_pages[pid, :, (length - 1) % page] = float("nan")
+    # the launcher's choice; one block; a cluster of 4 and of 8; several clusters a tile, which
+    # merge through global memory (twice on the same buffers: the counters must be zero again);
+    # clusters of one block
+    for split, repeats in ((None, 1), ((1, 1, 2048), 1), ((4, 1, 320), 1), ((8, 1, 192), 2),
+                           ((2, 3, 192), 3), ((1, 5, 256), 2), ((4, 2, 192), 1)):
+        got, k_after, v_after = run_decode_attention(
+            fx, qkv, heads, kv_heads, d, d ** -0.5, window, inv_freq, rot, writes, split=split,
+            repeats=repeats)
+        chunk = split
+        assert_close(got, want, dtype, f"decode attention split={split}")
+        # the pages afterwards: the tokens' keys and values where they belong, the rest untouched
+        # (NaN in free pages and beyond the sequences' ends included)
+        fresh = torch.zeros(fx.k_pages.shape[0], page, dtype=torch.bool)
+        for i, length in enumerate(kv_lens):
+            fresh[int(fx.block_table[fx.slots[i], (length - 1) // page]), (length - 1) % page] = True
+        for after, full in ((k_after, pages_full[0]), (v_after, pages_full[1])):
+            after, full = after.transpose(1, 2), full.transpose(1, 2)      # [pages, page, kv, d]
+            same = (after == full) | (torch.isnan(after) & torch.isnan(full))
+            assert same[~fresh].all(), f"pages after the decode kernel, chunk={chunk}"
+            assert_close(after[fresh], full[fresh], dtype, "the tokens' own keys and values")
+
+
 def test_attention_refuses_sizes_it_does_not_take():
     from distengine_b200.kernels.attention import AttentionLauncher
     with pytest.raises(ValueError, match="head sizes"):
