@@ -24,7 +24,8 @@
 //
 // Items (attention_plan): every tile has `cap` consecutive items (its chunks in ascending order,
 // padded with empty ones), `cap` a multiple of the cluster size; block (g, hk, rank) of the grid
-// takes item g * cluster + rank and kv head hk.
+// takes item g * cluster + rank and kv head hk.  In place of the partial slots, which this kernel
+// derives itself, an item carries the token's position and its sequence's slot.
 
 #include "common.cuh"
 
@@ -64,6 +65,21 @@ constexpr int SMEM_MERGE = OFF_BLK_L + ROWS * 4;
 constexpr int SMEM_BYTES = SMEM_TILES > SMEM_MERGE ? SMEM_TILES : SMEM_MERGE;
 static_assert(OFF_BLK_L + ROWS * 4 <= OFF_Q, "the merge area must not reach q (still in use)");
 
+#ifdef DECODE_TIMING
+// Debugging aid, compiled on request only: wall-clock stamps of one block's phases.
+__device__ unsigned long long decode_stamps[16];
+#define STAMP(k)                                                                      \
+    do {                                                                              \
+        if (blockIdx.x == DECODE_TIMING && threadIdx.x == 0) {                        \
+            unsigned long long t_;                                                    \
+            asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t_));                  \
+            decode_stamps[k] = t_;                                                    \
+        }                                                                             \
+    } while (0)
+#else
+#define STAMP(k) do { } while (0)
+#endif
+
 __global__ void __launch_bounds__(THREADS)
 attn_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int qkv_stride,
                    __nv_bfloat16* __restrict__ out, int out_stride,
@@ -75,6 +91,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int qkv_stride,
                    int* __restrict__ counters, const float* __restrict__ inv_freq, int rot,
                    int write_kv, int heads, int kv_heads, int page, float scale, int window,
                    int* __restrict__ status) {
+    (void)seq_slot;
+    (void)seq_pos0;                    // both come with the items
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(smem_raw + OFF_K);
     __nv_bfloat16* v_s = reinterpret_cast<__nv_bfloat16*>(smem_raw + OFF_V);
@@ -83,16 +101,20 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int qkv_stride,
     __nv_bfloat16* v_new = reinterpret_cast<__nv_bfloat16*>(smem_raw + OFF_VNEW);
     __shared__ int s_last;
 
+    STAMP(0);
     cg::cluster_group cluster = cg::this_cluster();
     const int csize = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
     const int group = blockIdx.x / csize;                 // (items' cluster, kv head)
     const int hk = group % kv_heads;
     const int item_index = (group / kv_heads) * csize + rank;
+    // the items of this kernel carry the token's position and its sequence's slot in place of
+    // the partial slots (one dependent read less before the first copies can be requested)
     const WorkItem it = items[item_index];
     const bool empty = it.kv_begin >= it.kv_end;          // padding: takes part in the merge only
     const int g = heads / kv_heads;
-    const int pos = seq_pos0[it.seq];                     // the token's position
-    const int slot = seq_slot[it.seq], tok = seq_qstart[it.seq];
+    const int pos = it.partial;                           // the token's position
+    const int slot = it.first_partial;
+    const int tok = seq_qstart[it.seq];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int wn = warp;
     const int gid = lane >> 2, tig = lane & 3;
@@ -145,7 +167,28 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int qkv_stride,
     if (k_lo + KT < hi) load_tile(k_lo + KT, 1);
     cp_async_commit();
 
+    // what does not depend on qkv: the angles' cosines and sines, the page the token's key goes to
+    const int half = rot / 2;
+    constexpr int TODO = (ROWS + 1) * (D / 2);            // pairs of 16 q rows and of the key
+    constexpr int PER = (TODO + THREADS - 1) / THREADS;
+    float cs[PER], sn[PER];
+#pragma unroll
+    for (int u = 0; u < PER; ++u) {
+        const int idx = threadIdx.x + u * THREADS;
+        const int r = idx / (D / 2), j = idx - r * (D / 2);
+        const bool rotated = !empty && j < half && inv_freq != nullptr &&
+                             (r < n_rows || (r == ROWS && new_key));
+        const float angle = rotated ? (float)pos * inv_freq[j] : 0.0f;
+        cs[u] = cosf(angle);
+        sn[u] = sinf(angle);
+    }
+    int write_page = -1;
+    if (new_key && it.row0 == 0 && threadIdx.x < 2 * CHUNKS)
+        write_page = block_table[(size_t)slot * table_stride + pos / page];
+
+    STAMP(1);
     pdl_wait();                                       // qkv is the previous kernel's output
+    STAMP(2);
 
     float o_acc[DT][4];
 #pragma unroll
@@ -160,11 +203,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int qkv_stride,
         // stay.  Every thread first requests all it needs (independent loads), then computes.
         const __nv_bfloat16* token = qkv + (size_t)tok * qkv_stride;
         {
-            const int half = rot / 2;
-            constexpr int TODO = (ROWS + 1) * (D / 2);            // pairs of 16 q rows and the key
-            constexpr int PER = (TODO + THREADS - 1) / THREADS;
             __nv_bfloat16 a[PER], bb[PER];
-            float freq[PER];
 #pragma unroll
             for (int u = 0; u < PER; ++u) {
                 const int idx = threadIdx.x + u * THREADS;
@@ -176,7 +215,6 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int qkv_stride,
                     token + (size_t)(r < ROWS ? hk * g + it.row0 + r : heads + hk) * D;
                 a[u] = live ? src[c0] : __float2bfloat16_rn(0.0f);
                 bb[u] = live ? src[c1] : __float2bfloat16_rn(0.0f);
-                freq[u] = (live && j < half && inv_freq) ? inv_freq[j] : 0.0f;
             }
             __nv_bfloat16 vn = __float2bfloat16_rn(0.0f);
             if (new_key && threadIdx.x < D)
@@ -190,10 +228,9 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int qkv_stride,
                 const int c0 = j < half ? j : rot + 2 * (j - half);
                 const int c1 = j < half ? j + half : c0 + 1;
                 if (j < half && inv_freq && (r < n_rows || r == ROWS)) {
-                    const float angle = (float)pos * freq[u];
                     float ra, rb;
-                    rope_rotate(__bfloat162float(a[u]), __bfloat162float(bb[u]), cosf(angle),
-                                sinf(angle), ra, rb);
+                    rope_rotate(__bfloat162float(a[u]), __bfloat162float(bb[u]), cs[u], sn[u], ra,
+                                rb);
                     dst[c0] = __float2bfloat16_rn(ra);
                     dst[c1] = __float2bfloat16_rn(rb);
                 } else {                              // unrotated features; zeros beyond the group
@@ -211,12 +248,11 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int qkv_stride,
 
         // the token's key and value into the cache: the block of the group's first rows does it
         if (new_key && it.row0 == 0 && threadIdx.x < 2 * CHUNKS) {
-            const int page_id = block_table[(size_t)slot * table_stride + pos / page];
-            if (page_id < 0 || page_id >= num_pages) {    // a table without a page here: record, skip
+            if (write_page < 0 || write_page >= num_pages) {  // no page here: record, skip
                 if (threadIdx.x == 0) atomicExch(status, 1);
             } else {
                 const size_t off =
-                    ((size_t)page_id * kv_heads + hk) * page * D + (size_t)(pos % page) * D;
+                    ((size_t)write_page * kv_heads + hk) * page * D + (size_t)(pos % page) * D;
                 const int ch = threadIdx.x % CHUNKS;
                 if (threadIdx.x < CHUNKS)
                     *reinterpret_cast<uint4*>(k_pages + off + ch * 8) =
@@ -228,6 +264,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int qkv_stride,
         }
         fill_new(k_lo, 0);
         fill_new(k_lo + KT, 1);
+        STAMP(3);
 
         unsigned qf[D / 16][4];
 #pragma unroll
@@ -331,6 +368,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int qkv_stride,
         }
     }
     cp_async_wait<0>();
+    STAMP(4);
     pdl_trigger();
 
 #pragma unroll
@@ -362,63 +400,81 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int qkv_stride,
         }
     }
     __syncthreads();
-    for (int e = threadIdx.x; e < ROWS * D; e += THREADS) {
-        const int r = e / D, dd = e - r * D;
+    {
+        // thread (row, column group): the row's factors once, then D / 8 columns
+        static_assert(THREADS == ROWS * 8, "one thread per row and eighth of the columns");
+        const int r = threadIdx.x >> 3, c0 = (threadIdx.x & 7) * (D / 8);
         float m = -INFINITY;
 #pragma unroll
         for (int w = 0; w < WN; ++w) m = fmaxf(m, red_m[w * ROWS + r]);
-        float l = 0.0f, acc = 0.0f;
+        float f[WN], l = 0.0f;
 #pragma unroll
         for (int w = 0; w < WN; ++w) {
             const float mw = red_m[w * ROWS + r];
-            if (mw == -INFINITY) continue;
-            const float f = exp2f((mw - m) * sl);
-            l += red_l[w * ROWS + r] * f;
-            acc += red_o[((size_t)w * ROWS + r) * D + dd] * f;
+            f[w] = mw == -INFINITY ? 0.0f : fast_exp2((mw - m) * sl);
+            l += red_l[w * ROWS + r] * f[w];
         }
-        blk_o[r * D + dd] = acc;
-        if (dd == 0) {
+#pragma unroll
+        for (int i = 0; i < D / 16; ++i) {
+            float2 acc = make_float2(0.0f, 0.0f);
+#pragma unroll
+            for (int w = 0; w < WN; ++w) {
+                const float2 v = *reinterpret_cast<const float2*>(
+                    red_o + ((size_t)w * ROWS + r) * D + c0 + 2 * i);
+                acc.x = fmaf(v.x, f[w], acc.x);
+                acc.y = fmaf(v.y, f[w], acc.y);
+            }
+            *reinterpret_cast<float2*>(blk_o + r * D + c0 + 2 * i) = acc;
+        }
+        if ((threadIdx.x & 7) == 0) {
             blk_m[r] = m;                                      // exp2 domain (times sl)
             blk_l[r] = l;
         }
     }
 
-    // ---- the cluster's result: every block merges a slice of (row, feature) from all blocks
+    // ---- the cluster's result: every block merges a slice of (row, pair of features) from all
+    STAMP(5);
     cluster.sync();
-    const int total = n_rows * D;
+    STAMP(6);
+    const int total = n_rows * D / 2;                          // pairs
     const int slice = (total + csize - 1) / csize;
     const int e_end = min(total, (rank + 1) * slice);
     const bool final_here = clusters_per_tile == 1;
     const size_t part_slot = (size_t)it.tile * clusters_per_tile + cluster_in_tile;
     __nv_bfloat16* out_token = out + (size_t)tok * out_stride + (size_t)(hk * g + it.row0) * D;
     for (int e = rank * slice + threadIdx.x; e < e_end; e += THREADS) {
-        const int r = e / D, dd = e - r * D;
-        float mc[MAX_CLUSTER], lc[MAX_CLUSTER], ac[MAX_CLUSTER];
+        const int r = e / (D / 2), dd = 2 * (e - r * (D / 2));
+        float mc[MAX_CLUSTER], lc[MAX_CLUSTER];
+        float2 ac[MAX_CLUSTER];
 #pragma unroll
         for (int c = 0; c < MAX_CLUSTER; ++c) {               // independent remote loads
-            mc[c] = -INFINITY; lc[c] = 0.0f; ac[c] = 0.0f;
+            mc[c] = -INFINITY; lc[c] = 0.0f; ac[c] = make_float2(0.0f, 0.0f);
             if (c < csize) {
                 mc[c] = cluster.map_shared_rank(blk_m, c)[r];
                 lc[c] = cluster.map_shared_rank(blk_l, c)[r];
-                ac[c] = cluster.map_shared_rank(blk_o, c)[r * D + dd];
+                ac[c] = *reinterpret_cast<const float2*>(cluster.map_shared_rank(blk_o, c) +
+                                                         r * D + dd);
             }
         }
         float m = -INFINITY;
 #pragma unroll
         for (int c = 0; c < MAX_CLUSTER; ++c) m = fmaxf(m, mc[c]);
-        float l = 0.0f, acc = 0.0f;
+        float l = 0.0f;
+        float2 acc = make_float2(0.0f, 0.0f);
 #pragma unroll
         for (int c = 0; c < MAX_CLUSTER; ++c) {
             if (mc[c] == -INFINITY) continue;                 // no visible key there (or no block)
-            const float f = exp2f((mc[c] - m) * sl);
+            const float f = fast_exp2((mc[c] - m) * sl);
             l += lc[c] * f;
-            acc = fmaf(ac[c], f, acc);
+            acc.x = fmaf(ac[c].x, f, acc.x);
+            acc.y = fmaf(ac[c].y, f, acc.y);
         }
         if (final_here) {
-            out_token[r * D + dd] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            *reinterpret_cast<unsigned*>(out_token + r * D + dd) = pack_bf16(acc.x * inv, acc.y * inv);
         } else {
             const size_t idx = (part_slot * kv_heads + hk) * ROWS + r;
-            partial_acc[idx * D + dd] = acc;
+            *reinterpret_cast<float2*>(partial_acc + idx * D + dd) = acc;
             if (dd == 0) {
                 partial_ml[idx * 2] = m * scale;              // natural-log domain, as merged
                 partial_ml[idx * 2 + 1] = l;
@@ -426,7 +482,9 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int qkv_stride,
         }
     }
     if (!final_here) __threadfence();
+    STAMP(7);
     cluster.sync();                    // nobody leaves while its shared memory may still be read
+    STAMP(8);
     if (final_here || rank != 0) return;
 
     // ---- several clusters a tile: the one that finishes last merges their partial results, in
@@ -445,7 +503,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int qkv_stride,
     __threadfence();
     const size_t step = (size_t)kv_heads * ROWS;                   // from one slot to the next
     const size_t row0_idx = ((size_t)it.tile * clusters_per_tile * kv_heads + hk) * ROWS;
-    for (int e = threadIdx.x; e < total; e += THREADS) {
+    for (int e = threadIdx.x; e < n_rows * D; e += THREADS) {
         const int r = e / D, dd = e - r * D;
         const size_t idx0 = row0_idx + r;
         float m = -INFINITY;
@@ -485,6 +543,11 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int qkv_stride,
 
 }  // namespace
 
+#ifdef DECODE_TIMING
+DE_EXPORT int de_attn_decode_stamps(unsigned long long* host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, decode_stamps, sizeof(decode_stamps));
+}
+#endif
 DE_EXPORT int de_attn_decode_head_dim() { return D; }
 DE_EXPORT int de_attn_decode_max_cluster() { return MAX_CLUSTER; }
 

@@ -61,11 +61,13 @@ static inline int de_check(cudaError_t e) { return e == cudaSuccess ? 0 : (int)e
 // of the step writes (or reads while this one writes); it returns once the preceding kernel has
 // completed and its writes are visible.  Before that a kernel may only do index arithmetic and read
 // weights and the step's arrays, which no kernel writes.  pdl_trigger() tells the scheduler that
-// the next kernel may be launched; kernels call it when their main loop is done, before they write
-// their outputs (measured on B200: triggering at the start of every kernel made decode steps 10%
-// slower than no overlap at all, triggering late makes them 3% faster).  Every kernel calls
-// pdl_wait() on all paths, so completion is transitive along the stream.  Without the launch
-// attribute both calls do nothing.
+// the next kernel may be launched; most kernels call it when their main loop is done, before they
+// write their outputs (measured on B200: triggering at the start of every kernel made decode steps
+// 10% slower than no overlap at all, because the waiting blocks took the place of blocks of the
+// running kernel that had not started yet; triggering late made them 3% faster).  The decode
+// products, whose blocks are all resident at once, trigger right after their first loads.  Every
+// kernel calls pdl_wait() on all paths, so completion is transitive along the stream.  Without
+// the launch attribute both calls do nothing.
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void pdl_trigger() {
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");

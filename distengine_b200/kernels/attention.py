@@ -119,7 +119,12 @@ class AttentionLauncher:
             cap = (need + cluster - 1) // cluster * cluster
         plan = build_plan(host.seq_qlen, host.seq_pos0, self.group, self.kv_heads, rows,
                           self.window, chunk, cap, sort=False)
-        prep.add(f"{self.key}/decode/items", plan.items)
+        # the kernel derives the partial slots itself; their fields carry the token's position
+        # and the sequence's slot instead
+        items = plan.items
+        items[:, 4] = host.seq_pos0[items[:, 0]]
+        items[:, 5] = host.seq_slot[items[:, 0]]
+        prep.add(f"{self.key}/decode/items", items)
         prep.notes[self.key] = ()
         prep.notes[self.key + "/decode"] = (tiles, cluster, cap)
 

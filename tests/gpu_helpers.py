@@ -130,7 +130,8 @@ def run_decode_attention(fx: PagedFixture, qkv, heads, kv_heads, head_dim, scale
     pos0 = np.array([length - 1 for length in fx.kv_lens], dtype=np.int32)
     qstart = np.arange(n, dtype=np.int32)
     launcher = AttentionLauncher(dtype, heads, kv_heads, head_dim, scale, window)
-    prep = StepPrep(SimpleNamespace(seq_qlen=qlen, seq_pos0=pos0))
+    prep = StepPrep(SimpleNamespace(seq_qlen=qlen, seq_pos0=pos0,
+                                    seq_slot=np.array(fx.slots, dtype=np.int32)))
     launcher.prepare(prep, force_split=split)
     k_pages, v_pages, table = fx.to_device()
     t = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(dev)
