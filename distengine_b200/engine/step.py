@@ -293,5 +293,8 @@ class StepRunner:
         code = int(self.status.item())
         if code != 0:
             self.status.zero_()
-            raise KernelStatusError(f"a kernel reported status {code}: a token's position had no "
-                                    f"page in its request's block table")
+            what = {1: "a token's position had no page in its request's block table",
+                    3: "a bounded wait inside a tcgen05 kernel ran out",
+                    4: "a tcgen05 kernel found its shared memory misaligned"}.get(
+                        code, "unknown code")
+            raise KernelStatusError(f"a kernel reported status {code}: {what}")

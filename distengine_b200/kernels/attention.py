@@ -130,15 +130,17 @@ class AttentionLauncher:
 
     def prepare(self, prep, force_chunk: "int | None" = None,
                 force_cap: "int | None" = None, force_shape: "str | None" = None,
-                force_split: "tuple[int, int, int] | None" = None) -> None:
+                force_split: "tuple[int, int, int] | None" = None,
+                allow_decode: bool = True) -> None:
         """Add this step's work lists to ``prep`` (once per step for all layers of this shape).
-        The ``force_*`` arguments pin the chunk size, the chunk cap and the tile shape; tests use
+        The ``force_*`` arguments pin the chunk size, the chunk cap and the tile shape, and
+        ``allow_decode`` false keeps a step of single tokens on the general kernels; tests use
         them to reach every path at small sizes."""
         if self.key in prep.notes:
             return
         host = prep.host
         one_each = bool(len(host.seq_qlen)) and bool((host.seq_qlen == 1).all())
-        if self.fused_decode and one_each and force_shape is None:
+        if self.fused_decode and one_each and force_shape is None and allow_decode:
             self._prepare_decode(prep, force_split)
             return
         prep.notes[self.key + "/decode"] = None

@@ -43,6 +43,7 @@ SIGNATURES: dict[str, dict[str, list]] = {
     },
     "gemm_tcgen05": {
         "de_gemm_tcgen05": [P, I, P, I, P, I, I, I, I, I, I, P, P],
+        "de_gemm_tcgen05_tile": [I, I, I], "de_gemm_tcgen05_sms": [],
     },
     "decode_fused": {
         "de_decode_fused_head_dim": [], "de_decode_fused_max_tokens": [],

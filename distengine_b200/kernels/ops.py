@@ -162,14 +162,42 @@ def _small_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
             and w.data_ptr() % 16 == 0)
 
 
+TCGEN05_ROWS = 1024     # from this many rows on, products go to this package's tcgen05 kernel
+_tile_fits: dict[tuple[int, int], bool] = {}
+
+
+def _tcgen05_fits(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
+    """Whether a plain product of this shape goes to this package's tcgen05 kernel: many rows, and
+    a shape whose tiles fill the SMs in whole rounds with wide tiles.  (Measured on B200 against
+    cuBLAS at 2,048 rows: equal or within 4% where this holds, up to a third slower where the
+    tiles have to be narrow or the last round is nearly empty; with few rows cuBLAS splits k,
+    which this kernel does not.)"""
+    m, n = x.shape[0], w.shape[0]
+    if (m < TCGEN05_ROWS or x.shape[1] % 8 or x.stride(0) % 8 or w.stride(0) % 8 or x.stride(1) != 1
+            or w.stride(1) != 1 or x.data_ptr() % 16 or w.data_ptr() % 16):
+        return False
+    key = (m, n)
+    fits = _tile_fits.get(key)
+    if fits is None:
+        lib = library.load("gemm_tcgen05")
+        bn, sms = lib.de_gemm_tcgen05_tile(m, n, 0), lib.de_gemm_tcgen05_sms()
+        tiles = -(-m // 128) * -(-n // bn)
+        rounds = -(-tiles // sms)
+        fits = _tile_fits[key] = bn >= 192 and m * n >= 0.75 * rounds * sms * 128 * bn
+    return fits
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, out: "torch.Tensor | None" = None,
-           out_dtype: "torch.dtype | None" = None) -> torch.Tensor:
+           out_dtype: "torch.dtype | None" = None,
+           status: "torch.Tensor | None" = None) -> torch.Tensor:
     """x @ w^T, float32 accumulation.
 
     float32: this package's own CUDA-core kernel (true 32-bit).  bfloat16 with up to 32 rows
     (decode steps): this package's weight-streaming kernel (``csrc/linear_small.cu``).  bfloat16
-    with more rows: the library matrix product (cuBLAS through torch), where the reference calls a
-    library too (src/layers/linear.py:19-20).  The output is bfloat16 or float32."""
+    with a thousand rows or more in a shape that suits it: this package's tcgen05 kernel
+    (``csrc/gemm_tcgen05.cu``).  Otherwise the library matrix product (cuBLAS through torch),
+    where the reference calls a library too (src/layers/linear.py:19-20).  The output is bfloat16
+    or float32.  ``status`` (int32 [1]): where the tcgen05 kernel records a wait that ran out."""
     out_dtype = out_dtype or (out.dtype if out is not None else x.dtype)
     if out is None:
         out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=x.device)
@@ -189,6 +217,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: "torch.Tensor | None" = None,
                                    out.data_ptr(), out.stride(0), x.shape[0], w.shape[0],
                                    x.shape[1], int(out.dtype == torch.float32), 0, _stream()),
                "linear_small")
+    elif _tcgen05_fits(x, w, out):
+        gemm_tcgen05(x, w, out, status=status)
     elif out.dtype == torch.bfloat16:
         torch.mm(x, w.t(), out=out)
     else:
@@ -196,11 +226,28 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: "torch.Tensor | None" = None,
     return out
 
 
+def gated_needs_scratch(x: torch.Tensor, w_gate_up: torch.Tensor) -> bool:
+    """Whether ``linear_gated`` forms the [gate | up] product in memory for these operands: not
+    for bfloat16 with up to 32 rows (weight-streaming kernel) or with a thousand rows or more
+    (tcgen05 kernel; with fewer rows its tiles leave most SMs idle and the library product plus
+    the activation kernel is faster)."""
+    if x.dtype != torch.bfloat16 or w_gate_up.dtype != torch.bfloat16:
+        return True
+    if _small_ok(x, w_gate_up):
+        return False
+    return not (x.shape[0] >= TCGEN05_ROWS and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0
+                and w_gate_up.stride(0) % 8 == 0 and x.stride(1) == 1
+                and w_gate_up.stride(1) == 1 and x.data_ptr() % 16 == 0
+                and w_gate_up.data_ptr() % 16 == 0)
+
+
 def linear_gated(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor,
-                 scratch: "torch.Tensor | None" = None) -> torch.Tensor:
+                 scratch: "torch.Tensor | None" = None,
+                 status: "torch.Tensor | None" = None) -> torch.Tensor:
     """out[n, i] = silu(x . gate_i) * (x . up_i) for w_gate_up = [gate rows; up rows] of shape
-    [2 inner, k].  Up to 32 rows: one kernel (the product's epilogue applies the activation).
-    More rows: the product into ``scratch`` [N, 2 inner], then ``silu_mul``."""
+    [2 inner, k].  bfloat16: one kernel whose epilogue applies the activation, the
+    weight-streaming one up to 32 rows, the tcgen05 one beyond.  float32 (or operands that are not
+    16-byte aligned): the product into ``scratch`` [N, 2 inner], then ``silu_mul``."""
     inner = w_gate_up.shape[0] // 2
     _need(tuple(out.shape) == (x.shape[0], inner), "linear_gated: out must be [N, inner]")
     if x.shape[0] == 0:
@@ -211,6 +258,8 @@ def linear_gated(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor,
                                    w_gate_up.stride(0), out.data_ptr(), out.stride(0), x.shape[0],
                                    inner, x.shape[1], 0, 1, _stream()), "linear_small (gated)")
         return out
+    if not gated_needs_scratch(x, w_gate_up) and out.stride(1) == 1 and out.dtype == x.dtype:
+        return gemm_tcgen05(x, w_gate_up, out, gated=True, status=status)
     if scratch is None:
         scratch = torch.empty((x.shape[0], 2 * inner), dtype=x.dtype, device=x.device)
     linear(x, w_gate_up, out=scratch)

@@ -68,7 +68,7 @@ class PagedAttention(Mixer):
             raise ValueError("attention needs a paged key/value cache")
         n, d = x.shape[0], self.head_dim
         qkv = ctx.buffer("attention.qkv", (n, (self.heads + 2 * self.kv_heads) * d))
-        ops.linear(x, self.w_qkv, out=qkv)
+        ops.linear(x, self.w_qkv, out=qkv, status=ctx.status)
         self.position.apply(qkv[:, : self.heads * d].view(n, self.heads, d),
                             qkv[:, self.heads * d: (self.heads + self.kv_heads) * d]
                             .view(n, self.kv_heads, d), ctx)
@@ -84,7 +84,7 @@ class PagedAttention(Mixer):
                               cache.block_table, cache.writes, ctx.status)
             self.kernels.run(qkv, out, cache.k_pages, cache.v_pages, cache.block_table, ctx)
         branch = ctx.buffer("attention.out", (n, self.width))
-        ops.linear(out, self.w_o, out=branch)
+        ops.linear(out, self.w_o, out=branch, status=ctx.status)
         return branch
 
 

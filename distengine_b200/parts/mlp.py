@@ -36,11 +36,11 @@ class GatedMLP(FeedForward):
         n = x.shape[0]
         act = ctx.buffer("mlp.act", (n, self.inner))
         scratch = None
-        if n > ops.SMALL_ROWS or self.dtype != torch.bfloat16:
+        if ops.gated_needs_scratch(x, self.w_gate_up):
             scratch = ctx.buffer("mlp.gate_up", (n, 2 * self.inner))
-        ops.linear_gated(x, self.w_gate_up, act, scratch)
+        ops.linear_gated(x, self.w_gate_up, act, scratch, status=ctx.status)
         out = ctx.buffer("mlp.out", (n, self.width))
-        ops.linear(act, self.w_down, out=out)
+        ops.linear(act, self.w_down, out=out, status=ctx.status)
         return out
 
 

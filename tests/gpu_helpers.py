@@ -96,7 +96,8 @@ def run_paged_attention(fx: PagedFixture, q_list, heads, kv_heads, head_dim, sca
     qstart = (np.cumsum(qlen) - qlen).astype(np.int32)
     launcher = AttentionLauncher(dtype, heads, kv_heads, head_dim, scale, window)
     prep = StepPrep(SimpleNamespace(seq_qlen=qlen, seq_pos0=pos0))
-    launcher.prepare(prep, force_chunk=chunk, force_cap=chunks_cap, force_shape=shape)
+    launcher.prepare(prep, force_chunk=chunk, force_cap=chunks_cap, force_shape=shape,
+                     allow_decode=False)
     q = torch.cat([t.reshape(t.shape[0], heads * head_dim) for t in q_list]).to(dev, dtype)
     # q lives inside a wider row, as in the engine's fused qkv buffer
     wide = torch.zeros(q.shape[0], heads * head_dim + 2 * kv_heads * head_dim, dtype=dtype,

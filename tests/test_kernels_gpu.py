@@ -431,7 +431,8 @@ def test_linear_gated(m, k, inner):
 
 
 @pytest.mark.parametrize("m,n,k", [(128, 128, 64), (77, 200, 120), (300, 384, 2048), (129, 331 + 5, 72),
-                                   (2048, 256, 5632), (33, 50, 8)])
+                                   (2048, 256, 5632), (33, 50, 8), (2048, 2560, 136),
+                                   (1500, 4100, 72), (20000, 264, 64)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_gemm_tcgen05(m, n, k, out_dtype):
     """The tensor-memory matrix product (TMA + tcgen05.mma) at sizes that are no multiples of its
@@ -448,7 +449,8 @@ def test_gemm_tcgen05(m, n, k, out_dtype):
     assert_close(out, want, out_dtype, "gemm_tcgen05")
 
 
-@pytest.mark.parametrize("m,inner,k", [(128, 64, 64), (200, 192, 120), (2048, 5632, 2048), (40, 320, 264)])
+@pytest.mark.parametrize("m,inner,k", [(128, 64, 64), (200, 192, 120), (2048, 5632, 2048), (40, 320, 264),
+                                       (1100, 176, 72), (3000, 1000, 40)])
 def test_gemm_tcgen05_gated(m, inner, k):
     """silu(gate) * up as the epilogue of the tensor-memory product."""
     ops = _ops()
@@ -462,3 +464,33 @@ def test_gemm_tcgen05_gated(m, inner, k):
     gate = plain.plain_linear(x.float(), w[:inner].float(), torch.bfloat16)
     up = plain.plain_linear(x.float(), w[inner:].float(), torch.bfloat16)
     assert_close(out, plain.plain_swiglu(gate, up, torch.bfloat16), torch.bfloat16, "gated tcgen05")
+
+
+def test_products_of_many_rows_take_the_tcgen05_kernel():
+    """From a thousand rows on, ``linear`` (in a shape that suits it) and ``linear_gated`` run this
+    package's tcgen05 kernel: the results agree with the plain product, and the kernel library is
+    the one that was called (its launch leaves the status word alone, the output is written)."""
+    from distengine_b200.kernels import ops as raw
+    ops = _ops()
+    g = torch.Generator().manual_seed(11)
+    m, k, n, inner = 2048, 64, 2048, 200
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(n, k, generator=g) * 0.1).to(torch.bfloat16)
+    dev_x, dev_w = x.to(DEV), w.to(DEV)
+    out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    assert raw._tcgen05_fits(dev_x, dev_w, out)
+    assert not raw._tcgen05_fits(dev_x[:1000], dev_w, out[:1000])
+    assert not raw._tcgen05_fits(dev_x, dev_w[:2560 - 2048 + 100], out[:, :612])
+    ops.linear(dev_x, dev_w, out=out)
+    assert_close(out, plain.plain_linear(x.float(), w.float(), torch.bfloat16), torch.bfloat16,
+                 "linear, many rows")
+    wg = (torch.randn(2 * inner, k, generator=g) * 0.1).to(torch.bfloat16)
+    dev_wg = wg.to(DEV)
+    assert not raw.gated_needs_scratch(dev_x, dev_wg)
+    assert raw.gated_needs_scratch(dev_x[:500], dev_wg)
+    act = torch.full((m, inner), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.linear_gated(dev_x, dev_wg, act)
+    gate = plain.plain_linear(x.float(), wg[:inner].float(), torch.bfloat16)
+    up = plain.plain_linear(x.float(), wg[inner:].float(), torch.bfloat16)
+    assert_close(act, plain.plain_swiglu(gate, up, torch.bfloat16), torch.bfloat16,
+                 "linear_gated, many rows")
