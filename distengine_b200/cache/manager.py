@@ -304,6 +304,14 @@ class CacheManager:
                     row[p] = -1
                 self._mark(group, live.slot, gone[0], gone[-1] + 1)
 
+    def rewind(self, request_id: str, length: int) -> None:
+        """Forget the tokens beyond ``length`` (a step that was launched ahead and is not used).
+        Pages stay with the request: it is about to need them again."""
+        live = self._get(request_id)
+        if length > live.length or length < 0:
+            raise ValueError("rewind goes back, and not below zero")
+        live.length = length
+
     def release(self, request_id: str) -> None:
         """Give back everything the request holds: its pages in every group and its slot."""
         live = self._get(request_id)

@@ -58,7 +58,7 @@ class Engine:
                                    max_len, self.model.config.vocabulary)
         self.sampler = Sampler(device, cfg.decode_batch_size)
         self.completed: deque[dict] = deque()
-        self._ahead = None                      # the next step, prepared while this one runs
+        self._flying = None                     # (plan, sampler ticket) of the step that is running
         self.requests: dict[str, Request] = {}
         self.steps = 0
         self.tokens_fed = 0
@@ -73,38 +73,42 @@ class Engine:
         self.requests[request_id] = request
 
     def has_pending(self) -> bool:
-        return self.scheduler.has_pending()
+        return self._flying is not None or self.scheduler.has_pending()
 
     def step(self) -> list[dict]:
-        """Plan one batch, run it, sample, finish and free.  Returns the completions of this
+        """Finish one batch: sample, account, finish and free.  Returns the completions of that
         step (they are also queued for ``drain_completed``).
 
-        While the GPU runs the step, the host already prepares the next one if it can be foreseen
-        (all running requests keep decoding): positions, pages and work lists do not depend on
-        the tokens being sampled; those are filled in when they arrive.  The plan itself always
-        comes from the scheduler; a prepared step is used only when it is exactly that plan."""
-        plan = self.scheduler.schedule()
-        if not plan.entries:
-            return []
-        entries = [StepEntry(e.request.request_id, e.tokens,
-                             [len(e.tokens) - 1] if e.sample else []) for e in plan.entries]
-        ahead, self._ahead = self._ahead, None
-        if ahead is not None and self._same_step(ahead, entries):
-            prepared = ahead
-            self.runner.set_tokens(prepared, [e.tokens[0] for e in entries])
-        else:
-            sampling = [e.request for e in plan.entries if e.sample]
-            # the sampled token will sit at position num_computed + len(portion) = len(known tokens)
-            extra = pack_sampling([r.temperature for r in sampling], [r.seed for r in sampling],
-                                  [r.num_tokens for r in sampling])
-            prepared = self.runner.prepare(entries, extra)
-        logits = self.runner.launch(prepared)
-        self.sampler.launch(logits, self.runner.last_arrays)
-        self._ahead = self._prepare_ahead(plan)               # host work under the GPU's
-        tokens = self.sampler.wait()
+        The GPU is kept one step ahead of the host.  While a step runs, the step after it is
+        started if it can be foreseen (all running requests keep decoding one token): its
+        positions, pages and work lists do not depend on the tokens being sampled, and the token
+        ids themselves go from the sampler's output to the next step's input on the device.  Only
+        then does the host wait for this step's tokens.  The plan always comes from the
+        scheduler: a step that was started ahead counts only if it is exactly the plan the
+        scheduler makes once the tokens are known; otherwise (an end-of-sequence token, a new
+        request, a preemption) its cache lengths are taken back and the scheduler's plan runs.
+        When this method returns, the next step, if there is one, is already running."""
+        flying, self._flying = self._flying, None
+        if flying is None:
+            flying = self._start(self.scheduler.schedule())
+            if flying is None:
+                return []
+        plan, ticket = flying
+        ahead = self._start_ahead(plan)                       # before this step's tokens are known
+        tokens = self.sampler.wait(ticket)
         self.steps += 1
         self.tokens_fed += plan.num_tokens
         finished = self.scheduler.update(plan, tokens)
+        if self.scheduler.has_pending():
+            following = self.scheduler.schedule()
+            if ahead is not None and self._same_step(ahead[0], following):
+                self._flying = (following, ahead[1])
+            else:
+                if ahead is not None:
+                    self._take_back(ahead[0])
+                self._flying = self._start(following)
+        elif ahead is not None:
+            self._take_back(ahead[0])
         done = []
         for request in finished:
             record = request.snapshot()
@@ -113,18 +117,31 @@ class Engine:
             done.append(record)
         return done
 
-    @staticmethod
-    def _same_step(prepared, entries: list[StepEntry]) -> bool:
-        mine = prepared.entries
-        return (len(mine) == len(entries)
-                and all(a.request_id == b.request_id and len(b.tokens) == 1 and b.want == [0]
-                        for a, b in zip(mine, entries)))
+    def _start(self, plan):
+        """Prepare and launch the scheduler's plan and its sampling; (plan, ticket) or None."""
+        if not plan.entries:
+            return None
+        entries = [StepEntry(e.request.request_id, e.tokens,
+                             [len(e.tokens) - 1] if e.sample else []) for e in plan.entries]
+        sampling = [e.request for e in plan.entries if e.sample]
+        # the sampled token will sit at position num_computed + len(portion) = len(known tokens)
+        extra = pack_sampling([r.temperature for r in sampling], [r.seed for r in sampling],
+                              [r.num_tokens for r in sampling])
+        logits = self.runner.launch(self.runner.prepare(entries, extra))
+        return plan, self.sampler.launch(logits, self.runner.last_arrays)
 
-    def _prepare_ahead(self, plan):
-        """The next step's host half, if it is sure to be one decoded token for every running
-        request: every running request samples in this step, none reaches its length limit,
-        nothing waits, and the pages are there.  An end-of-sequence token or anything else that
-        changes the plan simply leaves the prepared step unused."""
+    @staticmethod
+    def _same_step(prepared, plan) -> bool:
+        mine = prepared.entries
+        return (len(mine) == len(plan.entries)
+                and all(a.request_id == b.request.request_id and len(b.tokens) == 1 and b.sample
+                        for a, b in zip(mine, plan.entries)))
+
+    def _start_ahead(self, plan):
+        """Launch the step after ``plan`` (which is running) if it is sure to be one decoded
+        token for every running request: every running request samples in ``plan``, none reaches
+        its length limit, nothing waits, and the pages are there.  Returns (prepared step,
+        sampler ticket) or None."""
         sched = self.scheduler
         running = sched.running
         if (sched.waiting or not running or len(plan.entries) != len(running)
@@ -141,7 +158,19 @@ class Engine:
         entries = [StepEntry(r.request_id, [0], [0]) for r in running]
         extra = pack_sampling([r.temperature for r in running], [r.seed for r in running],
                               [r.num_tokens + 1 for r in running])
-        return self.runner.prepare(entries, extra)
+        prepared = self.runner.prepare(entries, extra)
+        # the ids this step feeds are the ones the running step is about to sample
+        logits = self.runner.launch(prepared, token_source=self.sampler.ids[: len(running)])
+        return prepared, self.sampler.launch(logits, self.runner.last_arrays)
+
+    def _take_back(self, prepared) -> None:
+        """A step that was started ahead and is not the scheduler's plan: its requests that still
+        run go back to the length they had (what it wrote to the cache lies beyond it and is
+        written again).  The GPU work itself is lost."""
+        for entry in prepared.entries:
+            if self.cache.has(entry.request_id):
+                self.cache.rewind(entry.request_id,
+                                  self.cache.length(entry.request_id) - len(entry.tokens))
 
     def drain_completed(self) -> list[dict]:
         results = list(self.completed)

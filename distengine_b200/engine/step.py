@@ -198,13 +198,21 @@ class StepRunner:
         views, offsets, total, arrays = self._stage(host, prep)
         return PreparedStep(entries, host, prep, graph_shape, fused, views, offsets, total)
 
-    def launch(self, prepared: "PreparedStep") -> torch.Tensor:
+    def launch(self, prepared: "PreparedStep",
+               token_source: "torch.Tensor | None" = None) -> torch.Tensor:
         """The device half: upload the prepared arrays, run the model, advance the cache's
         lengths.  Returns logits float32 [wanted, vocabulary] on the device, in the order of the
-        entries and of each entry's ``want``; the tensor is reused by the next step."""
+        entries and of each entry's ``want``; the tensor is reused by the next step.
+        ``token_source`` (int32 on the device, one id per token of the step): the token ids are
+        taken from there instead of from the prepared arrays - ids that an earlier kernel in the
+        stream produces and the host has not seen yet."""
         host, prep, views = prepared.host, prepared.prep, prepared.views
         total = prepared.total
         self._dev_meta[:total].copy_(self._host_meta[:total], non_blocking=True)
+        if token_source is not None:
+            if token_source.dtype != torch.int32 or token_source.numel() != host.n_tokens:
+                raise ValueError("token_source must hold one int32 id for each token of the step")
+            views["token_ids"].copy_(token_source.view(-1), non_blocking=True)
         self.cache.flush_tables()
         self._uploaded.record()
         self._upload_pending = True

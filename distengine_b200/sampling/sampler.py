@@ -28,23 +28,32 @@ def pack_sampling(temperatures: list[float], seeds: list[int], positions: list[i
 
 
 class Sampler:
+    """Two launches may be outstanding (the engine starts the next step before it has read this
+    step's ids): the ids travel to the host through two pinned buffers in turn."""
+
     def __init__(self, device: torch.device, max_rows: int) -> None:
         self.device = device
         self.ids = torch.zeros(max_rows, dtype=torch.int32, device=device)
-        self.host_ids = torch.zeros(max_rows, dtype=torch.int32).pin_memory()
-        self._done = torch.cuda.Event()
-        self._rows = 0
+        self.host_ids = [torch.zeros(max_rows, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._done = [torch.cuda.Event(), torch.cuda.Event()]
+        self._turn = 0
+        self._last = (0, 0)
 
-    def launch(self, logits: torch.Tensor, arrays: "dict[str, torch.Tensor] | None") -> int:
+    def launch(self, logits: torch.Tensor,
+               arrays: "dict[str, torch.Tensor] | None") -> "tuple[int, int]":
         """Start sampling the rows of ``logits`` [R, V] and the copy of the ids to the host;
-        returns R.  ``wait`` hands the ids out."""
+        returns a ticket for ``wait``.  The ids also stay on the device (``self.ids[:R]``) until
+        the next launch, for a step that is started before the host has seen them."""
         rows = logits.shape[0]
-        self._rows = rows
+        self._turn ^= 1
+        turn = self._turn
+        self._last = (turn, rows)
         if rows == 0:
-            return 0
+            return self._last
         if rows > self.ids.shape[0]:
             self.ids = torch.zeros(2 * rows, dtype=torch.int32, device=self.device)
-            self.host_ids = torch.zeros(2 * rows, dtype=torch.int32).pin_memory()
+        if rows > self.host_ids[turn].shape[0]:
+            self.host_ids[turn] = torch.zeros(2 * rows, dtype=torch.int32).pin_memory()
         out = self.ids[:rows]
         if arrays and "sampling/temperature" in arrays:
             ops.sample_rows(logits, out, arrays["sampling/temperature"].view(torch.float32),
@@ -52,18 +61,18 @@ class Sampler:
                             arrays["sampling/position"])
         else:
             ops.sample_rows(logits, out)
-        self.host_ids[:rows].copy_(out, non_blocking=True)
-        self._done.record()
-        return rows
+        self.host_ids[turn][:rows].copy_(out, non_blocking=True)
+        self._done[turn].record()
+        return self._last
 
-    def wait(self) -> list[int]:
-        """The ids of the last ``launch`` (synchronises with it)."""
-        if self._rows == 0:
+    def wait(self, ticket: "tuple[int, int] | None" = None) -> list[int]:
+        """The ids of a launch (the last one by default); synchronises with it."""
+        turn, rows = ticket or self._last
+        if rows == 0:
             return []
-        self._done.synchronize()
-        return self.host_ids[: self._rows].tolist()
+        self._done[turn].synchronize()
+        return self.host_ids[turn][:rows].tolist()
 
     def sample(self, logits: torch.Tensor, arrays: "dict[str, torch.Tensor] | None") -> list[int]:
         """Token ids for the rows of ``logits`` [R, V]; synchronises to bring them to the host."""
-        self.launch(logits, arrays)
-        return self.wait()
+        return self.wait(self.launch(logits, arrays))

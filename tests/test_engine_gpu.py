@@ -113,6 +113,32 @@ def test_submit_step_interface_and_eos(model_root):
     assert records["y"]["reason"] == "length" and len(records["y"]["generated_token_ids"]) == 2
 
 
+def test_a_step_started_ahead_is_taken_back_when_a_request_ends(model_root):
+    """The engine starts the next decode step before it has seen this step's tokens.  A request
+    that ends on an end-of-sequence token makes that step void for everyone: the others must go
+    on from the right length and give the tokens they give alone."""
+    spec, folder, config, weights, prompts = _setup("tiny_a", model_root)
+    engine = _engine(folder, spec, torch.float32)
+    alone = [plain.plain_generate(config, weights, p, 12) for p in prompts[:3]]
+    # request 0 ends when it produces its 5th token; the token must not occur earlier in its output
+    eos = alone[0][4]
+    cut = alone[0].index(eos) + 1
+    engine.submit("a", prompts[0], 12, eos_token_id=eos)
+    engine.submit("b", prompts[1], 12, eos_token_id=-1)
+    engine.submit("c", prompts[2], 12, eos_token_id=-1)
+    launched_ahead = 0
+    while engine.has_pending():
+        engine.step()
+        launched_ahead += engine._flying is not None
+    records = {r["request_id"]: r for r in engine.drain_completed()}
+    assert launched_ahead > 0
+    assert records["a"]["generated_token_ids"] == alone[0][:cut] and records["a"]["reason"] == "eos"
+    assert records["b"]["generated_token_ids"] == alone[1]
+    assert records["c"]["generated_token_ids"] == alone[2]
+    engine.cache.check_invariants()
+    assert engine.cache.num_free_pages() == engine.cache.num_pages
+
+
 def test_generate_greedy_function(model_root):
     from distengine_b200 import generate_greedy
     spec, folder, config, weights, prompts = _setup("tiny_a", model_root)
