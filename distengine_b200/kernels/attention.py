@@ -111,6 +111,14 @@ class AttentionLauncher:
         if self.window:
             span = min(span, self.window)
         cluster, clusters, chunk = force_split or choose_decode_split(tiles, self.kv_heads, span)
+        if force_split is None:
+            # the number of items is fixed by the cap (a replayed graph needs that); the chunk
+            # length follows the step's longest range, so that the items share it evenly
+            longest = int(host.seq_pos0.max()) + 1
+            if self.window:
+                longest = min(longest, self.window)
+            per_item = (longest + cluster * clusters - 1) // (cluster * clusters)
+            chunk = max((per_item + 63) // 64 * 64, 64)
         # chunks lie at absolute multiples of `chunk`: a window that starts inside one reaches
         # into one chunk more
         cap = clusters * cluster
