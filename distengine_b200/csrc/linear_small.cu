@@ -69,9 +69,12 @@ __host__ __device__ constexpr int blocks_per_round(int nt, int rows, bool gated)
 // NT: token tiles of 8 (rows of x <= 8 NT).  ROWS: weight rows per block (16 or 8).
 // GATED: silu(gate) * up epilogue.
 // PINGPONG: two rounds of weights in registers, one in use and one on its way (for long k; with a
-// single round it would only cost registers, and with them blocks per SM).
+// single round it would only cost registers, and with them blocks per SM).  The launch bounds keep
+// three blocks an SM for up to 8 tokens (two with PINGPONG): a decode step's products have 256 to
+// 352 blocks, which should all be resident at once.
 template <int NT, int ROWS, bool GATED, bool PINGPONG, typename OutT>
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(WARPS * 32,
+                                  PINGPONG ? (NT <= 2 ? 2 : 1) : (NT == 1 ? 3 : (NT == 2 ? 2 : 1)))
 linear_small_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ w,
                     int ldw, OutT* __restrict__ out, int ldo, int m_rows, int n_out, int k_dim) {
     constexpr int SETS = GATED ? 2 : 1;              // weight row sets per block
