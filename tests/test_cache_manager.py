@@ -68,6 +68,26 @@ def test_errors_follow_the_reference_classes():
         m.commit("a", -1)
 
 
+def test_rewind_takes_a_length_back_and_keeps_the_pages():
+    """A step that was launched ahead and is not used: the length goes back, the pages stay, and
+    the same tokens can be reserved and committed again."""
+    m = manager()
+    m.admit("a")
+    m.reserve([("a", 9)])
+    m.commit("a", 9)
+    free = m.num_free_pages()
+    m.rewind("a", 8)
+    assert m.length("a") == 8 and m.num_free_pages() == free
+    assert m.pages_needed("a", 9) == 0                      # the page of token 9 is still held
+    m.reserve([("a", 9)])
+    m.commit("a", 9)
+    with pytest.raises(ValueError):
+        m.rewind("a", 10)
+    m.check_invariants()
+    m.release("a")
+    assert m.num_free_pages() == m.num_pages
+
+
 def test_reserve_is_all_or_nothing():
     m = manager(pages=4)
     m.admit("a"), m.admit("b")
