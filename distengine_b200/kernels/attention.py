@@ -110,7 +110,8 @@ class AttentionLauncher:
             span = int(host.seq_pos0.max()) + 1
         if self.window:
             span = min(span, self.window)
-        cluster, clusters, chunk = force_split or choose_decode_split(tiles, self.kv_heads, span)
+        cluster, clusters, chunk = force_split or choose_decode_split(
+            tiles, self.kv_heads, span, int(os.environ.get("DISTENGINE_B200_DECODE_CLUSTER", "8")))
         if force_split is None:
             # the number of items is fixed by the cap (a replayed graph needs that); the chunk
             # length follows the step's longest range, so that the items share it evenly

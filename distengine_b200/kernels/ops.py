@@ -6,6 +6,8 @@ model code.
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import library
@@ -153,7 +155,10 @@ def gemm_f32(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
            "gemm_f32")
 
 
-SMALL_ROWS = 32          # up to this many tokens a product streams the weights through linear_small
+# Up to this many tokens a product streams the weights through linear_small (the kernel takes up
+# to 32; measured on B200 in decode steps, the library product is faster from 17 rows on: batch
+# 24: 1.17 against 1.42 ms a step, batch 32: 1.21 against 1.56; at 12 rows linear_small wins).
+SMALL_ROWS = int(os.environ.get("DISTENGINE_B200_SMALL_ROWS", "16"))
 
 
 def _small_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -192,7 +197,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: "torch.Tensor | None" = None,
            status: "torch.Tensor | None" = None) -> torch.Tensor:
     """x @ w^T, float32 accumulation.
 
-    float32: this package's own CUDA-core kernel (true 32-bit).  bfloat16 with up to 32 rows
+    float32: this package's own CUDA-core kernel (true 32-bit).  bfloat16 with up to 16 rows
     (decode steps): this package's weight-streaming kernel (``csrc/linear_small.cu``).  bfloat16
     with a thousand rows or more in a shape that suits it: this package's tcgen05 kernel
     (``csrc/gemm_tcgen05.cu``).  Otherwise the library matrix product (cuBLAS through torch),
@@ -228,7 +233,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: "torch.Tensor | None" = None,
 
 def gated_needs_scratch(x: torch.Tensor, w_gate_up: torch.Tensor) -> bool:
     """Whether ``linear_gated`` forms the [gate | up] product in memory for these operands: not
-    for bfloat16 with up to 32 rows (weight-streaming kernel) or with a thousand rows or more
+    for bfloat16 with up to 16 rows (weight-streaming kernel) or with a thousand rows or more
     (tcgen05 kernel; with fewer rows its tiles leave most SMs idle and the library product plus
     the activation kernel is faster)."""
     if x.dtype != torch.bfloat16 or w_gate_up.dtype != torch.bfloat16:
@@ -246,7 +251,7 @@ def linear_gated(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor,
                  status: "torch.Tensor | None" = None) -> torch.Tensor:
     """out[n, i] = silu(x . gate_i) * (x . up_i) for w_gate_up = [gate rows; up rows] of shape
     [2 inner, k].  bfloat16: one kernel whose epilogue applies the activation, the
-    weight-streaming one up to 32 rows, the tcgen05 one beyond.  float32 (or operands that are not
+    weight-streaming one up to 16 rows, the tcgen05 one from 1,024 rows.  float32 (or operands that are not
     16-byte aligned): the product into ``scratch`` [N, 2 inner], then ``silu_mul``."""
     inner = w_gate_up.shape[0] // 2
     _need(tuple(out.shape) == (x.shape[0], inner), "linear_gated: out must be [N, inner]")

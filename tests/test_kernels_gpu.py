@@ -394,13 +394,15 @@ def test_attention_refuses_sizes_it_does_not_take():
 
 @pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 31, 32])
 @pytest.mark.parametrize("k,n", [(64, 50), (2048, 2560), (120, 331), (5632, 2048), (200, 8)])
-def test_linear_small(m, k, n):
-    """The weight-streaming product for a handful of tokens, plain and with float32 output."""
+def test_linear_small(m, k, n, monkeypatch):
+    """The weight-streaming product for a handful of tokens, plain and with float32 output: all
+    row counts the kernel takes, also those that the engine gives to the library product."""
     ops = _ops()
     g = torch.Generator().manual_seed(m * k + n)
     x = torch.randn(m, k, generator=g).to(torch.bfloat16)
     w = (torch.randn(n, k, generator=g) * 0.1).to(torch.bfloat16)
     from distengine_b200.kernels import ops as raw
+    monkeypatch.setattr(raw, "SMALL_ROWS", 32)
     assert raw._small_ok(x.to(DEV), w.to(DEV))
     got = ops.linear(x.to(DEV), w.to(DEV))
     assert_close(got, plain.plain_linear(x.float(), w.float(), torch.bfloat16), torch.bfloat16,
@@ -417,8 +419,11 @@ def test_linear_small(m, k, n):
 
 @pytest.mark.parametrize("m", [1, 8, 13, 32, 40])
 @pytest.mark.parametrize("k,inner", [(64, 176), (2048, 5632), (120, 200)])
-def test_linear_gated(m, k, inner):
+@pytest.mark.parametrize("small_rows", [16, 32])
+def test_linear_gated(m, k, inner, small_rows, monkeypatch):
     """silu(gate) * up in the product's epilogue (up to 32 rows) and as product + kernel."""
+    from distengine_b200.kernels import ops as raw
+    monkeypatch.setattr(raw, "SMALL_ROWS", small_rows)
     ops = _ops()
     g = torch.Generator().manual_seed(m + k + inner)
     x = torch.randn(m, k, generator=g).to(torch.bfloat16)
