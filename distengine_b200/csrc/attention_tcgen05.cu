@@ -1,31 +1,32 @@
 // Attention over the paged cache for prompt portions on the 5th-generation tensor cores
 // (tcgen05.mma with accumulators in tensor memory, TMA page loads), bfloat16, head size 64.
 //
-// The same work items as attention_mma.cu's wide shape: a tile of 128 query rows of one sequence
-// and one kv head (rows are (token, query head of the group)) with a range of key positions.
-// A block of 256 threads owns the tile: row i is lane i of tensor memory, and two threads (in warps
-// w and w + 4, which may both read that lane) each serve half of its columns.
-// For every tile of 128 keys:
-//   1. thread 0 waits for the K and V pages of the tile (one TMA box per page, 128-byte swizzle,
-//      straight from the page pool through the block table) and issues s = q k^T: four
-//      tcgen05.mma (M 128, N 128, K 16), accumulator s in tensor memory;
-//   2. every thread reads its row of s (tcgen05.ld), masks (causal, window, range), keeps the
-//      running maximum and sum in float32, and writes p = exp2(...) as bfloat16 into shared
-//      memory in the operand layout (its row of two 64-key swizzled sub-tiles);
-//   3. thread 0 issues o_tile = p v: eight tcgen05.mma (M 128, N 64, K 16) with v as the
-//      "MN-major" operand, i.e. exactly as the cache stores it ([key][feature]);
-//   4. every thread reads its row of o_tile and adds it to its float32 output row, scaled by the
-//      change of the running maximum.
-// The tensor core runs ahead: s of the next tile is issued (into a second buffer in tensor memory)
-// before the softmax of the current one starts, and the pages are fetched two tiles ahead (three
-// stages).  One block per SM (145 KB of shared memory, all 512 tensor-memory columns).
+// A work item is 256 query rows of one sequence and one kv head (rows are (token, query head of
+// the group)) with a range of key positions.  A block owns it as two tiles of 128 rows, A and B,
+// that share every tile of 128 keys the block fetches.  Warps:
+//   * warps 0-3 are the softmax threads of tile A, warps 4-7 those of tile B: one thread per row
+//     (row i of a tile is lane i of tensor memory);
+//   * warp 8, one thread, issues the tensor-core work: s = q k^T (four tcgen05.mma M 128, N 128,
+//     K 16 per tile, accumulator in tensor memory) and o += p v (eight tcgen05.mma M 128, N 64,
+//     K 16, with v as the "MN-major" operand, i.e. exactly as the cache stores it,
+//     [key][feature]; o stays in tensor memory for the whole item);
+//   * warp 9 fetches the K and V pages of the key tiles (one TMA box per page, 128-byte swizzle,
+//     straight from the page pool through the block table), three tiles in flight.
+// For every key tile a softmax thread reads its row of s (128 values, tcgen05.ld) into registers,
+// tells the tensor-core thread that the columns are free (the scores of the next key tile are
+// then computed while this one is still being worked on), finds the row maximum and writes
+// p = exp2(...) as bfloat16 into shared memory in the operand layout.  The two row tiles go at
+// their own pace: the tensor-core thread polls what each is waiting for.  The running maximum a row's exponentials refer to is only raised when the true
+// maximum has grown by more than 2^8 since (then the row of o in tensor memory and the running
+// sum are rescaled); in between, values up to 2^8 are exact enough in float32 and in bfloat16's
+// range, and the quotient o / l does not depend on the reference.
 //
 // Formulas as in src/layers/attention.py:35-71 (scale after the product, causal mask, float32
 // softmax), grouped-query heads share the kv head's tiles.  Split key ranges write partial
 // results in the layout `de_attn_combine` merges.
 //
 // Every mbarrier wait is bounded (status 3, the block then runs to its end and frees its tensor
-// memory); no cluster launch, no multicast.
+// memory); no cluster launch, no multicast.  One block per SM (193 KB of shared memory).
 
 #include <cuda.h>
 
@@ -36,17 +37,17 @@ DE_DEFINE_PDL_SWITCH
 namespace {
 
 constexpr int D = 64;                  // head size: 128 bytes of bfloat16 = one swizzle row
-constexpr int ROWS = 128;              // query rows of a tile = lanes of tensor memory
+constexpr int TILE_ROWS = 128;         // query rows of a row tile = lanes of tensor memory
+constexpr int ROWS = 2 * TILE_ROWS;    // query rows of a work item: two row tiles
 constexpr int KT = 128;                // keys per tile
-constexpr int THREADS = 320;            // 8 softmax warps (two threads a row), tensor-core warp, copy warp
-constexpr int STAGES = 3;               // key/value tiles in flight
+constexpr int THREADS = 320;           // 2 x 4 softmax warps, tensor-core warp, copy warp
+constexpr int STAGES = 3;              // key/value tiles in flight
 constexpr int TILE_BYTES = 128 * 128;  // 128 rows of 128 bytes
-constexpr int TMEM_COLS = 512;         // s buffers at 0 and 128, p v buffers at 256 and 320
+constexpr int TMEM_COLS = 512;         // s of A at 0, of B at 128; o of A at 256, of B at 320
 constexpr unsigned SPIN_LIMIT = 20u * 1000u * 1000u;
-constexpr int SMEM_BYTES = (1 + 2 * STAGES + 4) * TILE_BYTES + 128 + 2048;
-#ifndef V_DESC_SWAP
-#define V_DESC_SWAP 0
-#endif
+// q of A and B, STAGES x (k, v), p of A and B (two sub-tiles of 64 keys each), barriers
+constexpr int SMEM_BYTES = (2 + 2 * STAGES + 4) * TILE_BYTES + 256;   // barriers: 14 x 8 + 4 bytes
+constexpr float RESCALE_AFTER = 8.0f;  // raise a row's reference maximum when it lags by 2^8
 
 struct WorkItem {
     int seq, row0, kv_begin, kv_end, partial, pad0, pad1, pad2;
@@ -81,6 +82,18 @@ __device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity, int* statu
     }
     atomicExch(status, 3);
     return false;
+}
+// Whether the phase with the given parity is complete; does not wait.
+__device__ __forceinline__ bool mbar_test(void* bar, unsigned parity) {
+    unsigned done;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return done != 0;
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, void* bar, int x,
                                             int y) {
@@ -126,6 +139,21 @@ __device__ __forceinline__ void tmem_load_32cols(unsigned taddr, unsigned (&r)[3
           "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
           "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_store_32cols(unsigned taddr, const unsigned (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+          "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]),
+          "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
+          "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+          "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_stores() {
+    asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
 }
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool pred) {
     const int bytes = pred ? 16 : 0;
@@ -204,18 +232,18 @@ attn_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
     // All shared memory is dynamic and starts at the block's window (1024-byte aligned, which the
     // swizzled tiles need; checked below).
     extern __shared__ __align__(1024) unsigned char smem_raw[];
-    unsigned char* q_s = smem_raw;                               // 16 KB
-    unsigned char* k_s = q_s + TILE_BYTES;                       // STAGES x 16 KB
+    unsigned char* q_s = smem_raw;                               // [2] x 16 KB: rows of A, of B
+    unsigned char* k_s = q_s + 2 * TILE_BYTES;                   // STAGES x 16 KB
     unsigned char* v_s = k_s + STAGES * TILE_BYTES;              // STAGES x 16 KB
-    unsigned char* p_s = v_s + STAGES * TILE_BYTES;              // 2 buffers x 2 sub-tiles (128 x 64 keys)
+    unsigned char* p_s = v_s + STAGES * TILE_BYTES;              // [2] x 2 sub-tiles (128 x 64 keys)
     unsigned long long* bars = reinterpret_cast<unsigned long long*>(p_s + 4 * TILE_BYTES);
     unsigned long long* kv_full = bars;                          // [STAGES] pages of a tile have landed
-    unsigned long long* s_done = bars + STAGES;                  // [2] scores are in tensor memory
-    unsigned long long* p_ready = bars + STAGES + 2;             // [2] p is in shared memory (256 arrivals)
-    unsigned long long* o_done = bars + STAGES + 4;              // [2] p v is in tensor memory
-    unsigned long long* o_free = bars + STAGES + 6;              // [2] p v has been read (256 arrivals)
-    unsigned& tmem_slot = *reinterpret_cast<unsigned*>(bars + STAGES + 8);
-    float* xch = reinterpret_cast<float*>(bars + STAGES + 9);    // [2][128] row values between halves
+    unsigned long long* kv_free = bars + STAGES;                 // [STAGES] the tile has been multiplied
+    unsigned long long* s_done = bars + 2 * STAGES;              // [2] scores of A / B are complete
+    unsigned long long* p_ready = bars + 2 * STAGES + 2;         // [2] p of A / B is written (128 arrivals)
+    unsigned long long* o_done = bars + 2 * STAGES + 4;          // [2] p v of A / B is complete
+    unsigned long long* s_free = bars + 2 * STAGES + 6;          // [2] s of A / B is in registers (128 arrivals)
+    unsigned& tmem_slot = *reinterpret_cast<unsigned*>(bars + 2 * STAGES + 8);
 
     // blocks are numbered item-major, so that the items run in the order the host gave them
     const WorkItem it = items[blockIdx.x / kv_heads];
@@ -224,12 +252,10 @@ attn_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
         pdl_wait();
         return;
     }
-    // Warps 0..7 are the softmax threads: thread (warp w, lane l) serves row 32 (w % 4) + l - the
-    // lane of tensor memory its warp may read - and the half w / 4 of that row's columns.  Warp 8
-    // issues the tensor-core work, warp 9 the copies.
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const bool driver = warp >= 8;
-    const int rowi = (warp & 3) * 32 + lane, half = (warp >> 2) & 1;
+    const bool softmax_thread = warp < 8;
+    const int x = softmax_thread ? warp >> 2 : 0;                // row tile: 0 = A, 1 = B
+    const int rowi = (warp & 3) * 32 + lane;                     // row within the row tile
     const int hk = blockIdx.x % kv_heads;
     const int g = heads / kv_heads;
     const int qlen = seq_qlen[it.seq], pos0 = seq_pos0[it.seq];
@@ -238,47 +264,58 @@ attn_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
 
     if (tid == 0) {
 #pragma unroll
-        for (int i = 0; i < STAGES; ++i) mbar_init(&kv_full[i], 1);
+        for (int i = 0; i < STAGES; ++i) {
+            mbar_init(&kv_full[i], 1);
+            mbar_init(&kv_free[i], 1);
+        }
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             mbar_init(&s_done[i], 1);
-            mbar_init(&p_ready[i], 256);
+            mbar_init(&p_ready[i], TILE_ROWS);
             mbar_init(&o_done[i], 1);
-            mbar_init(&o_free[i], 256);
+            mbar_init(&s_free[i], TILE_ROWS);
         }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     if (warp == 8) tmem_alloc(&tmem_slot, TMEM_COLS);
-    // stale shared memory must be finite: p = 0 times a NaN bit pattern would poison the product
-    for (int i = tid; i < 2 * STAGES * TILE_BYTES / 16; i += THREADS)
-        reinterpret_cast<uint4*>(k_s)[i] = make_uint4(0u, 0u, 0u, 0u);
 
-    const int r = it.row0 + rowi;
-    const bool live = !driver && r < rows_total;
+    // key range of the item and of each row tile: tile t holds the keys k_lo + 128 t .. + 127
+    int k_lo_true = it.kv_begin;
+    if (window > 0) k_lo_true = max(k_lo_true, pos0 + it.row0 / g - window + 1);
+    const int k_lo = (k_lo_true / KT) * KT;
+    int n_of[2], k_hi_of[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int first = it.row0 + i * TILE_ROWS;
+        n_of[i] = 0;
+        k_hi_of[i] = k_lo;
+        if (first < rows_total) {
+            const int last_row = min(first + TILE_ROWS, rows_total) - 1;
+            k_hi_of[i] = min(it.kv_end, pos0 + last_row / g + 1);
+            n_of[i] = max(0, (k_hi_of[i] - k_lo + KT - 1) / KT);
+        }
+    }
+    const int n_tiles = max(n_of[0], n_of[1]);
+    const int k_hi = max(k_hi_of[0], k_hi_of[1]);               // beyond it nothing is read
+
+    // this thread's row
+    const int r = it.row0 + x * TILE_ROWS + rowi;
+    const bool live = softmax_thread && r < rows_total;
     const int tok = live ? r / g : 0;
     const int hq = hk * g + (live ? r % g : 0);
     const int pos = live ? pos0 + tok : -1;
-
-    // key range of the tile and of this row
-    const int last_row = min(it.row0 + ROWS, rows_total) - 1;
-    const int max_pos = pos0 + last_row / g, min_pos = pos0 + it.row0 / g;
-    const int k_hi = min(it.kv_end, max_pos + 1);
-    int k_lo_true = it.kv_begin;
-    if (window > 0) k_lo_true = max(k_lo_true, min_pos - window + 1);
-    const int k_lo = (k_lo_true / KT) * KT;
     int lo = it.kv_begin;
     if (window > 0) lo = max(lo, pos - window + 1);
     const int hi = min(it.kv_end, pos + 1);                      // dead row: nothing visible
-    const int n_tiles = (k_hi - k_lo + KT - 1) / KT;
 
     pdl_wait();            // q, and the keys and values of this step's tokens, are just written
 
-    // q row into shared memory, operand layout (chunk index xor row % 8); each half four chunks
-    if (!driver) {
+    // q rows into shared memory, operand layout (chunk index xor row % 8)
+    if (softmax_thread) {
         const __nv_bfloat16* src = q + (size_t)(tok0 + tok) * q_stride + hq * D;
+        unsigned char* dst = q_s + x * TILE_BYTES + rowi * 128;
 #pragma unroll
-        for (int c = 4 * half; c < 4 * half + 4; ++c)
-            cp_async16(q_s + rowi * 128 + ((c ^ (rowi & 7)) << 4), src + c * 8, live);
+        for (int c = 0; c < 8; ++c) cp_async16(dst + ((c ^ (rowi & 7)) << 4), src + c * 8, live);
         asm volatile("cp.async.commit_group;\n" ::);
         asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     }
@@ -286,7 +323,7 @@ attn_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    const unsigned tmem = tmem_slot;          // s buffers at columns 0 and 128, p v at 256 and 320
+    const unsigned tmem = tmem_slot;
     const float sl = scale * 1.4426950408889634f;
     bool ok = true;
 
@@ -333,193 +370,253 @@ attn_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
             lookup(t);
             issue(t);
         }
-        for (int tile = 0; tile + STAGES < n_tiles; ++tile) {
-            lookup(tile + STAGES);
-            // the stage is free when p v of the tile that used it is complete
-            if (ok) ok = mbar_wait(&o_done[tile & 1], (tile >> 1) & 1, status);
+        for (int tile = STAGES; tile < n_tiles; ++tile) {
+            lookup(tile);
+            // the stage is free when the tile that used it has been multiplied
+            if (ok) ok = mbar_wait(&kv_free[tile % STAGES], ((tile / STAGES) - 1) & 1, status);
             ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (lane == 0) STAMP(1, tile, 4);
             if (ok) issue(tile % STAGES);
-            if (lane == 0) STAMP(1, tile, 5);
         }
     } else if (warp == 8) {
         // ------------------------------------------------------------------ tensor core
         constexpr unsigned idesc_s = instr_desc(128, 128, false);
         constexpr unsigned idesc_o = instr_desc(128, 64, true);
-        // s(tile) = q k^T into s buffer tile & 1
-        auto issue_scores = [&](int tile) {
-            const int stage = tile % STAGES;
-            if (ok) ok = mbar_wait(&kv_full[stage], (tile / STAGES) & 1, status);
-            if (ok) {
-                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                const unsigned long long a = desc_k_major(q_s);
-                const unsigned long long b = desc_k_major(k_s + stage * TILE_BYTES);
-#pragma unroll
-                for (int k = 0; k < D / 16; ++k)
-                    umma_bf16(tmem + 128 * (tile & 1), a + 2 * k, b + 2 * k, idesc_s, k > 0);
-            }
-            umma_commit(&s_done[tile & 1]);
-        };
         if (lane == 0) {
-            issue_scores(0);
-            if (n_tiles > 1) issue_scores(1);
-            for (int tile = 0; tile < n_tiles; ++tile) {
-                const int b = tile & 1, stage = tile % STAGES;
-                // p(tile) is written (so s(tile) has been read too) and the p v buffer is free
-                STAMP(1, tile, 0);
-                if (ok) ok = mbar_wait(&p_ready[b], (tile >> 1) & 1, status);
-                STAMP(1, tile, 1);
-                if (ok && tile >= 2) ok = mbar_wait(&o_free[b], ((tile >> 1) - 1) & 1, status);
+            // s of row tile i for key tile `tile` (its pages have landed: checked by the caller)
+            auto issue_scores = [&](int i, int tile) {
                 if (ok) {
-                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                    const unsigned long long vb = desc_mn_major(v_s + stage * TILE_BYTES);
-                    const unsigned long long pa = desc_k_major(p_s + 2 * b * TILE_BYTES);
+                    const unsigned long long a = desc_k_major(q_s + i * TILE_BYTES);
+                    const unsigned long long b = desc_k_major(k_s + (tile % STAGES) * TILE_BYTES);
 #pragma unroll
-                    for (int k = 0; k < KT / 16; ++k) {
-                        // 16 keys of p are 32 bytes inside a sub-tile row (the second sub-tile one
-                        // tile further); 16 keys of v are 2 groups of 8 rows = 2048 bytes
-                        umma_bf16(tmem + 256 + 64 * b,
-                                  pa + (unsigned long long)((k >> 2) * (TILE_BYTES >> 4) + 2 * (k & 3)),
-                                  vb + (unsigned long long)(k * 2048 >> 4), idesc_o, k > 0);
+                    for (int k = 0; k < D / 16; ++k)
+                        umma_bf16(tmem + 128 * i, a + 2 * k, b + 2 * k, idesc_s, k > 0);
+                }
+                umma_commit(&s_done[i]);
+            };
+            auto wait_tile = [&](int tile) {
+                if (ok) ok = mbar_wait(&kv_full[tile % STAGES], (tile / STAGES) & 1, status);
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            };
+            if (n_tiles > 0) wait_tile(0);
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+                if (n_of[i] > 0) issue_scores(i, 0);
+            // The two row tiles go at their own pace: this thread polls what each of them is
+            // waiting for and issues whatever has become possible -
+            //   the scores of a row tile's next key tile, once its threads hold the current
+            //   scores in registers and the key tile has landed;
+            //   o += p v, once its threads have written p;
+            // and hands a stage back to the copy warp when both row tiles' products that read it
+            // are issued.  A poll that finds nothing to do counts towards the iteration limit.
+            int s_next[2] = {1, 1}, pv_next[2] = {0, 0};
+            int freed = 0;
+            unsigned idle = 0;
+            while (ok) {
+                bool progress = false, busy = false;
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    if (pv_next[i] < n_of[i]) {
+                        busy = true;
+                        const int tile = pv_next[i];
+                        if (mbar_test(&p_ready[i], tile & 1)) {
+                            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                            const unsigned long long vb =
+                                desc_mn_major(v_s + (tile % STAGES) * TILE_BYTES);
+                            const unsigned long long pa = desc_k_major(p_s + 2 * i * TILE_BYTES);
+#pragma unroll
+                            for (int k = 0; k < KT / 16; ++k) {
+                                // 16 keys of p are 32 bytes inside a sub-tile row (the second
+                                // sub-tile one tile further); 16 keys of v are 2 groups of 8 rows
+                                // = 2048 bytes
+                                umma_bf16(tmem + 256 + 64 * i,
+                                          pa + (unsigned long long)((k >> 2) * (TILE_BYTES >> 4) +
+                                                                    2 * (k & 3)),
+                                          vb + (unsigned long long)(k * 2048 >> 4), idesc_o,
+                                          tile > 0 || k > 0);
+                            }
+                            umma_commit(&o_done[i]);
+                            STAMP(1, tile, 1 + 2 * i);
+                            ++pv_next[i];
+                            progress = true;
+                        }
+                    }
+                    if (s_next[i] < n_of[i]) {
+                        const int tile = s_next[i];
+                        if (mbar_test(&s_free[i], (tile - 1) & 1) &&
+                            mbar_test(&kv_full[tile % STAGES], (tile / STAGES) & 1)) {
+                            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                            issue_scores(i, tile);
+                            STAMP(1, tile, 2 * i);
+                            ++s_next[i];
+                            progress = true;
+                        }
                     }
                 }
-                umma_commit(&o_done[b]);
-                STAMP(1, tile, 2);
-                if (tile + 2 < n_tiles) issue_scores(tile + 2);          // into the s buffer just read
-                STAMP(1, tile, 3);
+                while (freed < n_tiles && (freed >= n_of[0] || pv_next[0] > freed) &&
+                       (freed >= n_of[1] || pv_next[1] > freed)) {
+                    umma_commit(&kv_free[freed % STAGES]);
+                    ++freed;
+                    progress = true;
+                }
+                if (!busy) break;
+                if (progress) {
+                    idle = 0;
+                } else if (++idle > SPIN_LIMIT) {
+                    atomicExch(status, 3);
+                    ok = false;
+                }
             }
         }
         __syncwarp();
-    } else {
+    } else if (n_of[x] > 0) {
         // ------------------------------------------------------------------ softmax threads
-        float o_row[32];                                         // this half's 32 output features
-#pragma unroll
-        for (int j = 0; j < 32; ++j) o_row[j] = 0.0f;
-        float m_run = -INFINITY, l_run = 0.0f;                   // l_run: this half's part of the sum
-        float corr_prev = 1.0f;                                  // rescale owed to the pending p v
         const unsigned lane_bits = (unsigned)((warp & 3) * 32) << 16;
-        auto take_product = [&](int tile) {                      // o_row += p v of `tile`
-            const int b = tile & 1;
-            if (ok) ok = mbar_wait(&o_done[b], (tile >> 1) & 1, status);
-            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            unsigned ov[32];
-            tmem_load_32cols(tmem + 256 + 64 * b + 32 * half + lane_bits, ov);
-            tmem_wait_loads();
-            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-            mbar_arrive(&o_free[b]);
-#pragma unroll
-            for (int j = 0; j < 32; ++j) o_row[j] = o_row[j] * corr_prev + __uint_as_float(ov[j]);
-        };
-        for (int tile = 0; tile < n_tiles; ++tile) {
-            const int b = tile & 1, stage = tile % STAGES;
+        const unsigned s_addr = tmem + 128 * x + lane_bits;
+        const unsigned o_addr = tmem + 256 + 64 * x + lane_bits;
+        unsigned char* p_row = p_s + 2 * x * TILE_BYTES + rowi * 128;
+        const int n_mine = n_of[x];
+        float m_ref = -INFINITY;                 // what the exponentials refer to
+        float l_run = 0.0f;
+        for (int tile = 0; tile < n_mine; ++tile) {
+            const int stage = tile % STAGES;
             const int kt = k_lo + tile * KT;
             if (tid == 0) STAMP(0, tile, 0);
-            if (ok) ok = mbar_wait(&s_done[b], (tile >> 1) & 1, status);
+            if (ok) ok = mbar_wait(&s_done[x], tile & 1, status);
             if (tid == 0) STAMP(0, tile, 1);
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            unsigned sv[2][32];
-            tmem_load_32cols(tmem + 128 * b + 64 * half + lane_bits, sv[0]);
-            tmem_load_32cols(tmem + 128 * b + 64 * half + 32 + lane_bits, sv[1]);
-            tmem_wait_loads();
-            if (tid == 0) STAMP(0, tile, 2);
             // only the tiles at the edges of the visible range (the diagonal, a window's start,
             // the first chunk) have keys to hide; the warp decides together
-            if (__any_sync(0xffffffffu, kt < lo || kt + KT > hi)) {
+            const bool masked = __any_sync(0xffffffffu, kt < lo || kt + KT > hi);
+            // ---- the row of s: 128 values, read once
+            unsigned sv[4][32];
 #pragma unroll
-                for (int c = 0; c < 2; ++c)
+            for (int c = 0; c < 4; ++c) tmem_load_32cols(s_addr + 32 * c, sv[c]);
+            tmem_wait_loads();
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            mbar_arrive(&s_free[x]);               // the next scores may overwrite these columns
+            if (masked) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
-                        const int key = kt + 64 * half + 32 * c + i;
-                        if (key < lo || key >= hi) sv[c][i] = 0xff800000u;       // -inf
+                        const int key = kt + 32 * c + i;
+                        if (key < lo || key >= hi) sv[c][i] = 0xff800000u;     // -inf
                     }
             }
-            float m_mine = -INFINITY;
+            float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains, not one
 #pragma unroll
-            for (int c = 0; c < 2; ++c)
+            for (int c = 0; c < 4; ++c)
 #pragma unroll
-                for (int i = 0; i < 32; ++i) m_mine = fmaxf(m_mine, __uint_as_float(sv[c][i]));
-            xch[(b * 2 + half) * 128 + rowi] = m_mine;
-            asm volatile("bar.sync 1, 256;\n" ::: "memory");     // the softmax threads only
+                for (int i = 0; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(sv[c][i]));
+            const float m_tile = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+            // p of the previous tile has been multiplied: its buffer is free, and o is at rest
+            if (tid == 0) STAMP(0, tile, 2);
+            if (tile > 0 && ok) ok = mbar_wait(&o_done[x], (tile - 1) & 1, status);
             if (tid == 0) STAMP(0, tile, 3);
-            const float m_new = fmaxf(m_run, fmaxf(m_mine, xch[(b * 2 + (half ^ 1)) * 128 + rowi]));
-            const float m_use = m_new == -INFINITY ? 0.0f : m_new;
-            const float corr = fast_exp2((m_run - m_use) * sl);
-            m_run = m_new;
-            const float m_off = -m_use * sl;
-            float l_add = 0.0f;
-            // p as bfloat16 into the operand layout: buffer b, sub-tile `half`, row rowi, 16-byte
-            // chunk (key / 8) xor (rowi % 8).  The buffer was read by p v of tile - 2, which is
-            // complete: its result was taken in the previous iteration.
+            // ---- raise the reference where the maximum has run away from it
+            const bool raise = m_tile > m_ref && (m_ref == -INFINITY ||
+                                                  (m_tile - m_ref) * sl > RESCALE_AFTER);
+            if (tile > 0 && __any_sync(0xffffffffu, raise && m_ref != -INFINITY)) {
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const float f = (raise && m_ref != -INFINITY) ? fast_exp2((m_ref - m_tile) * sl) : 1.0f;
+#pragma unroll 1
+                for (int c = 0; c < 2; ++c) {
+                    unsigned ov[32];
+                    tmem_load_32cols(o_addr + 32 * c, ov);
+                    tmem_wait_loads();
 #pragma unroll
-            for (int c = 0; c < 2; ++c)
+                    for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * f);
+                    tmem_store_32cols(o_addr + 32 * c, ov);
+                }
+                tmem_wait_stores();
+                l_run *= f;
+            }
+            if (raise) m_ref = m_tile;
+            // ---- p = exp2((s - reference) sl) as bfloat16 into the operand layout: row rowi of
+            // sub-tile (key / 64), 16-byte chunk ((key % 64) / 8) xor (rowi % 8)
+            const float m_off = m_ref == -INFINITY ? 0.0f : -m_ref * sl;
+            float l4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
 #pragma unroll
                 for (int i = 0; i < 32; i += 8) {
                     float p[8];
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         p[j] = fast_exp2(fmaf(__uint_as_float(sv[c][i + j]), sl, m_off));
-                        l_add += p[j];
+                        l4[j & 3] += p[j];
                     }
                     uint4 u;
                     u.x = pack2(p[0], p[1]); u.y = pack2(p[2], p[3]);
                     u.z = pack2(p[4], p[5]); u.w = pack2(p[6], p[7]);
-                    const int chunk = (32 * c + i) >> 3;
-                    *reinterpret_cast<uint4*>(p_s + (2 * b + half) * TILE_BYTES + rowi * 128 +
+                    const int chunk = ((32 * c + i) & 63) >> 3;
+                    *reinterpret_cast<uint4*>(p_row + (c >> 1) * TILE_BYTES +
                                               ((chunk ^ (rowi & 7)) << 4)) = u;
                 }
-            l_run = l_run * corr + l_add;
+            }
+            l_run += (l4[0] + l4[1]) + (l4[2] + l4[3]);
             if (tid == 0) STAMP(0, tile, 4);
             // Pages come whole: rows of v beyond the range (the rest of the last page, or keys
             // before a window) may hold anything, and 0 * NaN is NaN in the product.  Row rowi of
-            // the stage is key kt + rowi: zero it when it lies outside the tile's range.
+            // the stage is key kt + rowi: zero it when it lies outside the item's range.  (Both
+            // row tiles do this; they write the same zeros.)
             if (kt + rowi >= k_hi || kt + rowi < k_lo_true) {
                 if (ok) ok = mbar_wait(&kv_full[stage], (tile / STAGES) & 1, status);
-                uint4* vrow = reinterpret_cast<uint4*>(v_s + stage * TILE_BYTES + rowi * 128) + 4 * half;
+                uint4* vrow = reinterpret_cast<uint4*>(v_s + stage * TILE_BYTES + rowi * 128);
 #pragma unroll
-                for (int c = 0; c < 4; ++c) vrow[c] = make_uint4(0u, 0u, 0u, 0u);
+                for (int c = 0; c < 8; ++c) vrow[c] = make_uint4(0u, 0u, 0u, 0u);
             }
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-            mbar_arrive(&p_ready[b]);
+            mbar_arrive(&p_ready[x]);
             if (tid == 0) STAMP(0, tile, 5);
-            // while the tensor core multiplies p v of this tile: take the previous tile's result
-            if (tile >= 1) take_product(tile - 1);
-            if (tid == 0) STAMP(0, tile, 6);
-            corr_prev = corr;
         }
-        take_product(n_tiles - 1);
+        // ---- the item's last product, then the row goes out
+        if (ok) ok = mbar_wait(&o_done[x], (n_mine - 1) & 1, status);
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         pdl_trigger();
-
-        // the row's sum is the two halves' sums
-        xch[half * 128 + rowi] = l_run;
-        asm volatile("bar.sync 1, 256;\n" ::: "memory");
-        const float l_row = l_run + xch[(half ^ 1) * 128 + rowi];
-        if (ok && live) {
+        const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            unsigned ov[32];
+            tmem_load_32cols(o_addr + 32 * c, ov);
+            tmem_wait_loads();
+            if (!ok || !live) continue;
             if (it.partial < 0) {
-                const float inv = l_row > 0.0f ? 1.0f / l_row : 0.0f;
-                __nv_bfloat16* o = out + (size_t)(tok0 + tok) * out_stride + hq * D + 32 * half;
+                __nv_bfloat16* o = out + (size_t)(tok0 + tok) * out_stride + hq * D + 32 * c;
 #pragma unroll
                 for (int j = 0; j < 32; j += 8) {
                     uint4 u;
-                    u.x = pack2(o_row[j] * inv, o_row[j + 1] * inv);
-                    u.y = pack2(o_row[j + 2] * inv, o_row[j + 3] * inv);
-                    u.z = pack2(o_row[j + 4] * inv, o_row[j + 5] * inv);
-                    u.w = pack2(o_row[j + 6] * inv, o_row[j + 7] * inv);
+                    u.x = pack2(__uint_as_float(ov[j]) * inv, __uint_as_float(ov[j + 1]) * inv);
+                    u.y = pack2(__uint_as_float(ov[j + 2]) * inv, __uint_as_float(ov[j + 3]) * inv);
+                    u.z = pack2(__uint_as_float(ov[j + 4]) * inv, __uint_as_float(ov[j + 5]) * inv);
+                    u.w = pack2(__uint_as_float(ov[j + 6]) * inv, __uint_as_float(ov[j + 7]) * inv);
                     *reinterpret_cast<uint4*>(o + j) = u;
                 }
             } else {
-                const size_t idx = ((size_t)it.partial * kv_heads + hk) * ROWS + rowi;
-                float* pa = partial_acc + idx * D + 32 * half;
+                const size_t idx = ((size_t)it.partial * kv_heads + hk) * ROWS + x * TILE_ROWS + rowi;
+                float* pa = partial_acc + idx * D + 32 * c;
 #pragma unroll
                 for (int j = 0; j < 32; j += 4)
                     *reinterpret_cast<float4*>(pa + j) =
-                        make_float4(o_row[j], o_row[j + 1], o_row[j + 2], o_row[j + 3]);
-                if (half == 0) {
-                    partial_ml[idx * 2] = m_run * scale;          // natural-log domain, as merged
-                    partial_ml[idx * 2 + 1] = l_row;
+                        make_float4(__uint_as_float(ov[j]), __uint_as_float(ov[j + 1]),
+                                    __uint_as_float(ov[j + 2]), __uint_as_float(ov[j + 3]));
+                if (c == 0) {
+                    partial_ml[idx * 2] = m_ref * scale;          // natural-log domain, as merged
+                    partial_ml[idx * 2 + 1] = l_run;
                 }
             }
         }
+    } else if (live && it.partial >= 0) {
+        // a row tile without a key in this chunk: an empty partial result
+        const size_t idx = ((size_t)it.partial * kv_heads + hk) * ROWS + x * TILE_ROWS + rowi;
+        for (int j = 0; j < D; ++j) partial_acc[idx * D + j] = 0.0f;
+        partial_ml[idx * 2] = -INFINITY;
+        partial_ml[idx * 2 + 1] = 0.0f;
+    } else if (live) {
+        // no key at all for this row (cannot happen for a causal row, whose own key is visible)
+        __nv_bfloat16* o = out + (size_t)(tok0 + tok) * out_stride + hq * D;
+        for (int j = 0; j < D; ++j) o[j] = __float2bfloat16_rn(0.0f);
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();

@@ -68,7 +68,7 @@ class AttentionLauncher:
             # prompt portions at head size 64: the tcgen05 kernel (tensor-memory accumulators, TMA
             # page loads) takes the wide tiles; DISTENGINE_B200_ATTENTION=mma keeps the mma.sync one
             if head_dim == 64 and os.environ.get("DISTENGINE_B200_ATTENTION", "tcgen05") != "mma":
-                self.shapes[0] = _Shape("wide", 128, 2)
+                self.shapes[0] = _Shape("wide", 256, 2)
         else:
             self.shapes = [_Shape("rows8", 8, -1)]
             self.module = ("attention_simt", ())
@@ -78,6 +78,11 @@ class AttentionLauncher:
             "DISTENGINE_B200_DECODE_ATTENTION", "fused") != "split")
         self.key = (f"attention/{'mma' if self.tensor_cores else 'simt'}/{self.group}/"
                     f"{kv_heads}/{head_dim}/{self.window}")
+
+    def _blocks_per_sm(self) -> int:
+        """Blocks an SM holds at once: one of the tcgen05 kernel (it takes nearly all shared
+        memory), about two of the others; key ranges are only cut when there are fewer tiles."""
+        return 1 if any(shape.code == 2 for shape in self.shapes) else 2
 
     def modules(self) -> list[tuple[str, tuple[str, ...]]]:
         """The kernel libraries this launcher calls (to compile them side by side up front)."""
@@ -172,7 +177,7 @@ class AttentionLauncher:
             elif prep.graph_shape is not None:
                 cap = int(prep.graph_shape["context_cap"])
                 span = cap if not self.window else min(cap, self.window + int(host.seq_qlen.max()))
-                chunk = choose_chunk(total_tiles, self.kv_heads, span)
+                chunk = choose_chunk(total_tiles, self.kv_heads, span, self._blocks_per_sm())
                 if chunk:
                     chunks_cap = (span + chunk - 1) // chunk + (1 if self.window else 0)
             elif int(qlen.sum()):
@@ -180,7 +185,7 @@ class AttentionLauncher:
                 longest = int((host.seq_pos0[live] + qlen[live]).max())
                 if self.window:
                     longest = min(longest, self.window + int(qlen.max()))
-                chunk = choose_chunk(total_tiles, self.kv_heads, longest)
+                chunk = choose_chunk(total_tiles, self.kv_heads, longest, self._blocks_per_sm())
             plan = build_plan(qlen, host.seq_pos0, self.group, self.kv_heads, shape.rows,
                               self.window, chunk, chunks_cap)
             prep.add(f"{self.key}/{shape.name}/items", plan.items)

@@ -58,12 +58,14 @@ def _longest_first(items: np.ndarray, lo: np.ndarray) -> np.ndarray:
     return items[np.argsort(-keys, kind="stable")]
 
 
-def choose_chunk(num_tiles: int, kv_heads: int, longest: int) -> int:
-    """The largest chunk that still gives every SM about two blocks; 0: do not split."""
-    if num_tiles * kv_heads >= 2 * SM_COUNT:
+def choose_chunk(num_tiles: int, kv_heads: int, longest: int, blocks_per_sm: int = 2) -> int:
+    """The largest chunk that still gives every SM ``blocks_per_sm`` blocks (as many as the
+    kernel has resident at once); 0: do not split."""
+    wanted = blocks_per_sm * SM_COUNT
+    if num_tiles * kv_heads >= wanted:
         return 0
     for chunk in CHUNKS:
-        if num_tiles * kv_heads * ((longest + chunk - 1) // chunk) >= 2 * SM_COUNT:
+        if num_tiles * kv_heads * ((longest + chunk - 1) // chunk) >= wanted:
             return chunk
     return CHUNKS[-1]
 
