@@ -116,15 +116,17 @@ def test_attention_part_in_portions(dtype, heads, kv_heads, d, rot, window, page
     mixer.load(w)
     spec = mixer.cache_spec()
     assert (spec.kv_heads, spec.head_dim, spec.window) == (kv_heads, d, window)
-    xs = {"a": torch.randn(75, width, generator=g).to(dtype),
-          "b": torch.randn(40, width, generator=g).to(dtype)}
+    xs = {"a": torch.randn(75 + 7, width, generator=g).to(dtype),
+          "b": torch.randn(40 + 6, width, generator=g).to(dtype)}
     want = {rid: _plain_attention_part(x.float(), w, heads, kv_heads, d, rot, window, theta, dtype)
             for rid, x in xs.items()}
     h = PartHarness([mixer], [spec], dtype, page_size=page, num_pages=40)
     fed = {"a": 0, "b": 0}
     got = {"a": [], "b": []}
-    # portions of a beside portions and single tokens of b
-    for na, nb in [(30, 1), (2, 1), (1, 17), (25, 0), (17, 21)]:
+    # portions of a beside portions and single tokens of b; then steps of single tokens only
+    # (the one-launch decode kernel in bfloat16: rotation, cache write, window, pages that are
+    # gone from the table)
+    for na, nb in [(30, 1), (2, 1), (1, 17), (25, 0), (17, 21)] + [(1, 1)] * 6 + [(1, 0)]:
         entries = [(rid, n) for rid, n in (("a", na), ("b", nb)) if n]
         x = torch.cat([xs[rid][fed[rid]: fed[rid] + n] for rid, n in entries]).to(DEV)
         out = h.run(entries, lambda ctx, b: mixer.forward(x, ctx, b[0]).clone()).cpu()
