@@ -276,12 +276,13 @@ class CacheManager:
                 continue
             pages = group.pool.take(len(missing))
             table = group.tables[request_id]
-            row = group.host_table[slot]
+            if len(table) <= missing[-1]:
+                table.extend([-1] * (missing[-1] + 1 - len(table)))
             for logical, page in zip(missing, pages):
-                while len(table) <= logical:
-                    table.append(-1)
                 table[logical] = page
-                row[logical] = page
+            # one assignment for the row of the table that goes to the device (a prompt portion
+            # takes a hundred pages and more)
+            group.host_table.numpy()[slot, missing] = pages
             self._mark(group, slot, missing[0], missing[-1] + 1)
 
     def commit(self, request_id: str, new_len: int) -> None:

@@ -31,6 +31,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "tensor_maps.cuh"
 
 DE_DEFINE_PDL_SWITCH
 
@@ -624,36 +625,9 @@ attn_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
 }
 
 // ---------------------------------------------------------------------------------- host side
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiled encode_fn() {
-    static EncodeTiled fn = nullptr;
-    if (fn == nullptr) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult qr;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) ==
-                cudaSuccess && qr == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiled>(p);
-    }
-    return fn;
-}
-
-// the page pool of one layer as a matrix [pages * kv_heads * page rows, 64], boxes of one page
+// the pages of one layer as a matrix [pages * kv_heads * page, 64], boxes of one page
 int make_page_map(CUtensorMap* map, const void* pages, long long rows, int page) {
-    EncodeTiled encode = encode_fn();
-    if (encode == nullptr) return -20;
-    cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)D * 2};
-    cuuint32_t box[2] = {(cuuint32_t)D, (cuuint32_t)page};
-    cuuint32_t elem[2] = {1, 1};
-    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pages),
-                              dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : -21;
+    return tensor_maps::get(map, pages, rows, D, D, page, D);
 }
 
 }  // namespace
@@ -687,9 +661,13 @@ DE_EXPORT int de_attn_tcgen05(const void* q, int q_stride, void* out, int out_st
     code = make_page_map(&map_v, v_pages, rows, page);
     if (code) return code;
     const size_t smem = SMEM_BYTES;
-    cudaError_t e = cudaFuncSetAttribute(attn_tcgen05_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
+    static bool sized = false;                 // the attribute is set once
+    if (!sized) {
+        cudaError_t e = cudaFuncSetAttribute(attn_tcgen05_kernel,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        sized = true;
+    }
     dim3 grid((unsigned)num_items * (unsigned)kv_heads);
     return de_launch(attn_tcgen05_kernel, grid, dim3(THREADS), smem, (cudaStream_t)stream,
                      (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, map_k, map_v,

@@ -26,6 +26,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "tensor_maps.cuh"
 
 DE_DEFINE_PDL_SWITCH
 
@@ -339,36 +340,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
 }
 
 // ---------------------------------------------------------------------------------- host side
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiled encode_fn() {
-    static EncodeTiled fn = nullptr;
-    if (fn == nullptr) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
-                cudaSuccess && q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiled>(p);
-    }
-    return fn;
-}
-
 // A [rows, k] bfloat16 matrix with row stride ld (elements), boxes of box_rows x 64.
 int make_map(CUtensorMap* map, const void* base, int rows, int k, int ld, int box_rows) {
-    EncodeTiled encode = encode_fn();
-    if (encode == nullptr) return -20;
-    cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-    cuuint32_t elem[2] = {1, 1};
-    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base),
-                              dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : -21;
+    return tensor_maps::get(map, base, rows, k, ld, box_rows, BK);
 }
 
 int sm_count() {
@@ -423,9 +397,13 @@ int launch(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, i
     if (code) return code;
     const size_t smem = (size_t)SMEM_TILES + 1024;
     auto kernel = gemm_tcgen05_kernel<GATED, OutT>;
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)smem);
-    if (e != cudaSuccess) return (int)e;
+    static bool sized = false;                 // per instantiation: the attribute is set once
+    if (!sized) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        sized = true;
+    }
     const int out_cols = GATED ? bn / 2 : bn;
     const int tiles_m = (m_rows + BM - 1) / BM, tiles_n = (n_out + out_cols - 1) / out_cols;
     const int total = tiles_m * tiles_n;

@@ -29,12 +29,18 @@ class Workspace:
     def __init__(self, device: torch.device) -> None:
         self.device = device
         self._buffers: dict[str, torch.Tensor] = {}
+        # views handed out before, by (name, shape, dtype): a step asks for the same ones again
+        self._views: dict[tuple, torch.Tensor] = {}
         self.generation = 0          # grows whenever a buffer moves: captured graphs are stale then
 
     def get(self, name: str, shape: tuple[int, ...], dtype: torch.dtype,
             zero: bool = False) -> torch.Tensor:
         """``zero``: the buffer is zero when it is made (or made anew, larger); its users leave it
         zero after every use (counters that a kernel resets itself)."""
+        key = (name, shape, dtype)
+        view = self._views.get(key)
+        if view is not None:
+            return view
         count = 1
         for s in shape:
             count *= int(s)
@@ -45,7 +51,11 @@ class Workspace:
             buf = make(max(grow, 1), dtype=dtype, device=self.device)
             self._buffers[name] = buf
             self.generation += 1
-        return buf[:count].view(shape)
+            self._views = {k: v for k, v in self._views.items() if k[0] != name}
+        if len(self._views) > 4096:              # steps of ever new shapes: start over
+            self._views.clear()
+        view = self._views[key] = buf[:count].view(shape)
+        return view
 
     def bytes(self) -> int:
         return sum(b.numel() * b.element_size() for b in self._buffers.values())
