@@ -72,6 +72,56 @@ def test_replay_matches_plain(name, dtype_name, schedule, model_root):
         assert_close(got, reference[dtype][rid][positions], dtype, f"{name} {schedule} {rid}")
 
 
+LONG = dict(architectures=["LlamaForCausalLM"], vocab_size=211, hidden_size=120,
+            intermediate_size=136, num_hidden_layers=2, num_attention_heads=6,
+            num_key_value_heads=1, head_dim=48, rms_norm_eps=1e-5, rope_theta=1.0e6,
+            max_position_embeddings=6144, tie_word_embeddings=True)
+
+
+@pytest.mark.parametrize("dtype_name", ["float32", "bfloat16"])
+def test_long_context_then_decoding(dtype_name, model_root):
+    """4,500 tokens of context, fed in portions, then 24 tokens one by one: the decode steps cut
+    the key range into so many chunks that one thread-block cluster does not cover them (its
+    partial results are merged through global memory), prompt portions read thousands of keys
+    through the block table, and the pages of a second, short request lie in between."""
+    from distengine_b200.engine.replay import build_runner
+    from distengine_b200.kernels.attention_plan import choose_decode_split
+    from distengine_b200.weights import write_random_model
+    dtype = DTYPES[dtype_name]
+    folder = write_random_model(LONG, f"{model_root}/long-context", seed=21, norm_init="uniform")
+    config, weights = plain.load_model_folder(folder)
+    rng = np.random.default_rng(8)
+    requests = {"long": [int(t) for t in rng.integers(0, 211, size=4524)],
+                "short": [int(t) for t in rng.integers(0, 211, size=40)]}
+    assert choose_decode_split(1, 1, 4608)[1] > 1          # more than one cluster a tile
+    want = {rid: plain.plain_forward(config, weights, ids, dtype).numpy()
+            for rid, ids in requests.items()}
+    steps, at = [], 0
+    long_ids, short_ids = requests["long"], requests["short"]
+    for i, size in enumerate([1024, 20, 1500, 700, 1256]):        # 4,500 tokens in portions
+        entries = [{"id": "long", "tokens": long_ids[at: at + size], "want": [size - 1]}]
+        if i == 1:
+            entries.append({"id": "short", "tokens": short_ids[:30], "want": [29]})
+        steps.append({"step": len(steps), "entries": entries, "end": []})
+        at += size
+    for i in range(24):                                             # then token by token
+        entries = [{"id": "long", "tokens": [long_ids[at]], "want": [0]}]
+        if i < 10:
+            entries.append({"id": "short", "tokens": [short_ids[30 + i]], "want": [0]})
+        steps.append({"step": len(steps), "entries": entries,
+                      "end": ["short"] if i == 9 else (["long"] if i == 23 else [])})
+        at += 1
+    runner = build_runner(folder, dtype_name, 4608 + 64, page_size=32, poison_freed_pages=True)
+    with tempfile.TemporaryDirectory() as out:
+        th.replay_in_process(runner, steps, out)
+        rows = th.collect(steps, out, 211)
+    assert len(rows) == 5 + 1 + 24 + 10
+    for (rid, pos), got in rows.items():
+        assert_close(got, want[rid][pos], dtype, f"long context {rid}@{pos}")
+    runner.cache.check_invariants()
+    assert not runner.cache.live and runner.cache.num_free_pages() == runner.cache.num_pages
+
+
 @pytest.mark.parametrize("dtype_name", ["float32", "bfloat16"])
 def test_trace_run_program(dtype_name, model_root):
     """The program itself, as a user calls it: standard input, files, 'done' lines, exit 0."""
