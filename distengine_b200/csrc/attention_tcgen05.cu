@@ -37,17 +37,26 @@ DE_DEFINE_PDL_SWITCH
 
 namespace {
 
-constexpr int D = 64;                  // head size: 128 bytes of bfloat16 = one swizzle row
+#ifndef HEAD_DIM
+#define HEAD_DIM 64
+#endif
+constexpr int D = HEAD_DIM;            // head size: 64 or 128
+static_assert(D == 64 || D == 128, "the tcgen05 attention is built for head sizes 64 and 128");
+constexpr int KS = D / 64;             // 64-feature sub-tiles of a row (128 bytes = a swizzle row)
 constexpr int TILE_ROWS = 128;         // query rows of a row tile = lanes of tensor memory
-constexpr int ROWS = 2 * TILE_ROWS;    // query rows of a work item: two row tiles
+constexpr int NROW = D == 64 ? 2 : 1;  // row tiles of a work item (what shared memory has room for)
+constexpr int ROWS = NROW * TILE_ROWS; // query rows of a work item
 constexpr int KT = 128;                // keys per tile
-constexpr int THREADS = 320;           // 2 x 4 softmax warps, tensor-core warp, copy warp
-constexpr int STAGES = 3;              // key/value tiles in flight
-constexpr int TILE_BYTES = 128 * 128;  // 128 rows of 128 bytes
-constexpr int TMEM_COLS = 512;         // s of A at 0, of B at 128; o of A at 256, of B at 320
+constexpr int SOFTMAX_WARPS = 4 * NROW;
+constexpr int MMA_WARP = SOFTMAX_WARPS, COPY_WARP = SOFTMAX_WARPS + 1;
+constexpr int THREADS = (SOFTMAX_WARPS + 2) * 32;
+constexpr int STAGES = D == 64 ? 3 : 2;   // key/value tiles in flight
+constexpr int TILE_BYTES = 128 * 128;  // a sub-tile: 128 rows of 128 bytes
+constexpr int TMEM_COLS = 512;         // s of row tile x at 128 x; o of row tile x at 256 + D x
 constexpr unsigned SPIN_LIMIT = 20u * 1000u * 1000u;
-// q of A and B, STAGES x (k, v), p of A and B (two sub-tiles of 64 keys each), barriers
-constexpr int SMEM_BYTES = (2 + 2 * STAGES + 4) * TILE_BYTES + 256;   // barriers: 14 x 8 + 4 bytes
+// q of each row tile (KS sub-tiles), STAGES x (k, v) (KS sub-tiles each), p of each row tile (two
+// sub-tiles of 64 keys), barriers
+constexpr int SMEM_BYTES = (NROW * KS + 2 * STAGES * KS + 2 * NROW) * TILE_BYTES + 256;
 constexpr float RESCALE_AFTER = 8.0f;  // raise a row's reference maximum when it lags by 2^8
 
 struct WorkItem {
@@ -233,11 +242,12 @@ attn_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
     // All shared memory is dynamic and starts at the block's window (1024-byte aligned, which the
     // swizzled tiles need; checked below).
     extern __shared__ __align__(1024) unsigned char smem_raw[];
-    unsigned char* q_s = smem_raw;                               // [2] x 16 KB: rows of A, of B
-    unsigned char* k_s = q_s + 2 * TILE_BYTES;                   // STAGES x 16 KB
-    unsigned char* v_s = k_s + STAGES * TILE_BYTES;              // STAGES x 16 KB
-    unsigned char* p_s = v_s + STAGES * TILE_BYTES;              // [2] x 2 sub-tiles (128 x 64 keys)
-    unsigned long long* bars = reinterpret_cast<unsigned long long*>(p_s + 4 * TILE_BYTES);
+    unsigned char* q_s = smem_raw;                               // [NROW][KS] sub-tiles
+    unsigned char* k_s = q_s + NROW * KS * TILE_BYTES;           // [STAGES][KS] sub-tiles
+    unsigned char* v_s = k_s + STAGES * KS * TILE_BYTES;         // [STAGES][KS] sub-tiles
+    unsigned char* p_s = v_s + STAGES * KS * TILE_BYTES;         // [NROW][2] sub-tiles (128 x 64 keys)
+    unsigned long long* bars =
+        reinterpret_cast<unsigned long long*>(p_s + 2 * NROW * TILE_BYTES);
     unsigned long long* kv_full = bars;                          // [STAGES] pages of a tile have landed
     unsigned long long* kv_free = bars + STAGES;                 // [STAGES] the tile has been multiplied
     unsigned long long* s_done = bars + 2 * STAGES;              // [2] scores of A / B are complete
@@ -254,7 +264,7 @@ attn_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
         return;
     }
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const bool softmax_thread = warp < 8;
+    const bool softmax_thread = warp < SOFTMAX_WARPS;
     const int x = softmax_thread ? warp >> 2 : 0;                // row tile: 0 = A, 1 = B
     const int rowi = (warp & 3) * 32 + lane;                     // row within the row tile
     const int hk = blockIdx.x % kv_heads;
@@ -278,7 +288,7 @@ attn_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
         }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    if (warp == 8) tmem_alloc(&tmem_slot, TMEM_COLS);
+    if (warp == MMA_WARP) tmem_alloc(&tmem_slot, TMEM_COLS);
 
     // key range of the item and of each row tile: tile t holds the keys k_lo + 128 t .. + 127
     int k_lo_true = it.kv_begin;
@@ -290,7 +300,7 @@ attn_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
         const int first = it.row0 + i * TILE_ROWS;
         n_of[i] = 0;
         k_hi_of[i] = k_lo;
-        if (first < rows_total) {
+        if (i < NROW && first < rows_total) {
             const int last_row = min(first + TILE_ROWS, rows_total) - 1;
             k_hi_of[i] = min(it.kv_end, pos0 + last_row / g + 1);
             n_of[i] = max(0, (k_hi_of[i] - k_lo + KT - 1) / KT);
@@ -314,9 +324,11 @@ attn_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
     // q rows into shared memory, operand layout (chunk index xor row % 8)
     if (softmax_thread) {
         const __nv_bfloat16* src = q + (size_t)(tok0 + tok) * q_stride + hq * D;
-        unsigned char* dst = q_s + x * TILE_BYTES + rowi * 128;
+        unsigned char* dst = q_s + x * KS * TILE_BYTES + rowi * 128;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) cp_async16(dst + ((c ^ (rowi & 7)) << 4), src + c * 8, live);
+        for (int c = 0; c < D / 8; ++c)           // chunk c: sub-tile c / 8, place (c % 8) xor row
+            cp_async16(dst + (c >> 3) * TILE_BYTES + (((c & 7) ^ (rowi & 7)) << 4), src + c * 8,
+                       live);
         asm volatile("cp.async.commit_group;\n" ::);
         asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     }
@@ -328,7 +340,7 @@ attn_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
     const float sl = scale * 1.4426950408889634f;
     bool ok = true;
 
-    if (warp == 9) {
+    if (warp == COPY_WARP) {
         // ------------------------------------------------------------------ copies
         const int pages_per_tile = KT / page;
         const unsigned page_bytes = (unsigned)page * 128u;
@@ -353,7 +365,7 @@ attn_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
             unsigned bytes = 0;
 #pragma unroll
             for (int i = 0; i < 4; ++i)
-                if (id[i] >= 0) bytes += 2 * page_bytes;
+                if (id[i] >= 0) bytes += 2 * KS * page_bytes;
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) bytes += __shfl_xor_sync(0xffffffffu, bytes, o);
             if (lane == 0) mbar_expect_tx(&kv_full[stage], bytes);
@@ -363,8 +375,13 @@ attn_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
                 if (id[i] < 0) continue;
                 const int p = lane + 32 * i;
                 const int y = (id[i] * kv_heads + hk) * page;
-                tma_load_2d(k_s + stage * TILE_BYTES + p * page_bytes, &map_k, &kv_full[stage], 0, y);
-                tma_load_2d(v_s + stage * TILE_BYTES + p * page_bytes, &map_v, &kv_full[stage], 0, y);
+#pragma unroll
+                for (int sub = 0; sub < KS; ++sub) {          // 64 features a box
+                    tma_load_2d(k_s + (stage * KS + sub) * TILE_BYTES + p * page_bytes, &map_k,
+                                &kv_full[stage], 64 * sub, y);
+                    tma_load_2d(v_s + (stage * KS + sub) * TILE_BYTES + p * page_bytes, &map_v,
+                                &kv_full[stage], 64 * sub, y);
+                }
             }
         };
         for (int t = 0; t < STAGES && t < n_tiles; ++t) {
@@ -378,7 +395,7 @@ attn_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (ok) issue(tile % STAGES);
         }
-    } else if (warp == 8) {
+    } else if (warp == MMA_WARP) {
         // ------------------------------------------------------------------ tensor core
         constexpr unsigned idesc_s = instr_desc(128, 128, false);
         constexpr unsigned idesc_o = instr_desc(128, 64, true);
@@ -386,11 +403,15 @@ attn_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
             // s of row tile i for key tile `tile` (its pages have landed: checked by the caller)
             auto issue_scores = [&](int i, int tile) {
                 if (ok) {
-                    const unsigned long long a = desc_k_major(q_s + i * TILE_BYTES);
-                    const unsigned long long b = desc_k_major(k_s + (tile % STAGES) * TILE_BYTES);
 #pragma unroll
-                    for (int k = 0; k < D / 16; ++k)
-                        umma_bf16(tmem + 128 * i, a + 2 * k, b + 2 * k, idesc_s, k > 0);
+                    for (int sub = 0; sub < KS; ++sub) {
+                        const unsigned long long a = desc_k_major(q_s + (i * KS + sub) * TILE_BYTES);
+                        const unsigned long long b =
+                            desc_k_major(k_s + ((tile % STAGES) * KS + sub) * TILE_BYTES);
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            umma_bf16(tmem + 128 * i, a + 2 * k, b + 2 * k, idesc_s, sub > 0 || k > 0);
+                    }
                 }
                 umma_commit(&s_done[i]);
             };
@@ -421,19 +442,22 @@ attn_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
                         const int tile = pv_next[i];
                         if (mbar_test(&p_ready[i], tile & 1)) {
                             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                            const unsigned long long vb =
-                                desc_mn_major(v_s + (tile % STAGES) * TILE_BYTES);
                             const unsigned long long pa = desc_k_major(p_s + 2 * i * TILE_BYTES);
 #pragma unroll
-                            for (int k = 0; k < KT / 16; ++k) {
-                                // 16 keys of p are 32 bytes inside a sub-tile row (the second
-                                // sub-tile one tile further); 16 keys of v are 2 groups of 8 rows
-                                // = 2048 bytes
-                                umma_bf16(tmem + 256 + 64 * i,
-                                          pa + (unsigned long long)((k >> 2) * (TILE_BYTES >> 4) +
-                                                                    2 * (k & 3)),
-                                          vb + (unsigned long long)(k * 2048 >> 4), idesc_o,
-                                          tile > 0 || k > 0);
+                            for (int sub = 0; sub < KS; ++sub) {      // 64 output features at a time
+                                const unsigned long long vb = desc_mn_major(
+                                    v_s + ((tile % STAGES) * KS + sub) * TILE_BYTES);
+#pragma unroll
+                                for (int k = 0; k < KT / 16; ++k) {
+                                    // 16 keys of p are 32 bytes inside a sub-tile row (the second
+                                    // sub-tile one tile further); 16 keys of v are 2 groups of 8
+                                    // rows = 2048 bytes
+                                    umma_bf16(tmem + 256 + D * i + 64 * sub,
+                                              pa + (unsigned long long)((k >> 2) * (TILE_BYTES >> 4) +
+                                                                        2 * (k & 3)),
+                                              vb + (unsigned long long)(k * 2048 >> 4), idesc_o,
+                                              tile > 0 || k > 0);
+                                }
                             }
                             umma_commit(&o_done[i]);
                             STAMP(1, tile, 1 + 2 * i);
@@ -473,7 +497,7 @@ attn_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
         // ------------------------------------------------------------------ softmax threads
         const unsigned lane_bits = (unsigned)((warp & 3) * 32) << 16;
         const unsigned s_addr = tmem + 128 * x + lane_bits;
-        const unsigned o_addr = tmem + 256 + 64 * x + lane_bits;
+        const unsigned o_addr = tmem + 256 + D * x + lane_bits;
         unsigned char* p_row = p_s + 2 * x * TILE_BYTES + rowi * 128;
         const int n_mine = n_of[x];
         float m_ref = -INFINITY;                 // what the exponentials refer to
@@ -521,7 +545,7 @@ attn_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 const float f = (raise && m_ref != -INFINITY) ? fast_exp2((m_ref - m_tile) * sl) : 1.0f;
 #pragma unroll 1
-                for (int c = 0; c < 2; ++c) {
+                for (int c = 0; c < D / 32; ++c) {
                     unsigned ov[32];
                     tmem_load_32cols(o_addr + 32 * c, ov);
                     tmem_wait_loads();
@@ -563,9 +587,13 @@ attn_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
             // row tiles do this; they write the same zeros.)
             if (kt + rowi >= k_hi || kt + rowi < k_lo_true) {
                 if (ok) ok = mbar_wait(&kv_full[stage], (tile / STAGES) & 1, status);
-                uint4* vrow = reinterpret_cast<uint4*>(v_s + stage * TILE_BYTES + rowi * 128);
 #pragma unroll
-                for (int c = 0; c < 8; ++c) vrow[c] = make_uint4(0u, 0u, 0u, 0u);
+                for (int sub = 0; sub < KS; ++sub) {
+                    uint4* vrow = reinterpret_cast<uint4*>(v_s + (stage * KS + sub) * TILE_BYTES +
+                                                           rowi * 128);
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) vrow[c] = make_uint4(0u, 0u, 0u, 0u);
+                }
             }
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -578,7 +606,7 @@ attn_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
         pdl_trigger();
         const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
+        for (int c = 0; c < D / 32; ++c) {
             unsigned ov[32];
             tmem_load_32cols(o_addr + 32 * c, ov);
             tmem_wait_loads();
@@ -621,13 +649,13 @@ attn_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
-    if (warp == 8) tmem_dealloc(tmem, TMEM_COLS);
+    if (warp == MMA_WARP) tmem_dealloc(tmem, TMEM_COLS);
 }
 
 // ---------------------------------------------------------------------------------- host side
 // the pages of one layer as a matrix [pages * kv_heads * page, 64], boxes of one page
 int make_page_map(CUtensorMap* map, const void* pages, long long rows, int page) {
-    return tensor_maps::get(map, pages, rows, D, D, page, D);
+    return tensor_maps::get(map, pages, rows, D, D, page, 64);
 }
 
 }  // namespace

@@ -65,10 +65,13 @@ class AttentionLauncher:
                            _Shape("narrow", NARROW_ROWS, 1)]
             self.module = ("attention_mma", (f"HEAD_DIM={head_dim}",))
             self.decode_module = ("attention_decode", (f"HEAD_DIM={head_dim}",))
-            # prompt portions at head size 64: the tcgen05 kernel (tensor-memory accumulators, TMA
-            # page loads) takes the wide tiles; DISTENGINE_B200_ATTENTION=mma keeps the mma.sync one
-            if head_dim == 64 and os.environ.get("DISTENGINE_B200_ATTENTION", "tcgen05") != "mma":
-                self.shapes[0] = _Shape("wide", 256, 2)
+            # prompt portions at head sizes 64 and 128: the tcgen05 kernel (tensor-memory
+            # accumulators, TMA page loads) takes the wide tiles, two row tiles of 128 a block at
+            # head size 64 and one at 128; DISTENGINE_B200_ATTENTION=mma keeps the mma.sync one
+            self.tcgen05_module = ("attention_tcgen05", (f"HEAD_DIM={head_dim}",))
+            if (head_dim in (64, 128)
+                    and os.environ.get("DISTENGINE_B200_ATTENTION", "tcgen05") != "mma"):
+                self.shapes[0] = _Shape("wide", 256 if head_dim == 64 else 128, 2)
         else:
             self.shapes = [_Shape("rows8", 8, -1)]
             self.module = ("attention_simt", ())
@@ -88,7 +91,7 @@ class AttentionLauncher:
         """The kernel libraries this launcher calls (to compile them side by side up front)."""
         extra = [self.decode_module] if self.fused_decode else []
         if any(shape.code == 2 for shape in self.shapes):
-            extra.append(("attention_tcgen05", ()))
+            extra.append(self.tcgen05_module)
         return [self.module, ("attention_simt", ())] + extra
 
     # ------------------------------------------------------------------ host side
@@ -219,7 +222,7 @@ class AttentionLauncher:
                 rows = num_partials * self.kv_heads * shape.rows
                 acc = ctx.buffer(f"attention.partial_acc.{shape.name}", (rows * d,), torch.float32)
                 ml = ctx.buffer(f"attention.partial_ml.{shape.name}", (rows * 2,), torch.float32)
-            module = ("attention_tcgen05", ()) if shape.code == 2 else self.module
+            module = self.tcgen05_module if shape.code == 2 else self.module
             launch_items(shape.code, module, q, out, k_pages, v_pages, block_table,
                          ctx.seq_slot, ctx.seq_qstart, ctx.seq_qlen, ctx.seq_pos0, items, combine,
                          shape.rows, acc, ml, self.heads, self.kv_heads, d, self.scale, self.window,

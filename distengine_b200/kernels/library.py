@@ -72,8 +72,10 @@ def default_build_requests() -> list[tuple[str, tuple[str, ...]]]:
     """Every module; the per-head-size attention for the head sizes of common models."""
     requests = [(module, ()) for module in _build.MODULES
                 if module in SIGNATURES
-                and module not in ("attention_mma", "attention_decode", "decode_fused")]
+                and module not in ("attention_mma", "attention_decode", "decode_fused",
+                                   "attention_tcgen05")]
     return (requests + [("attention_mma", (f"HEAD_DIM={d}",)) for d in (64, 128)]
+            + [("attention_tcgen05", (f"HEAD_DIM={d}",)) for d in (64, 128)]
             + [("attention_decode", (f"HEAD_DIM={d}",)) for d in (64, 128)]
             + [("decode_fused", (f"HEAD_DIM={d}",)) for d in (64, 128)])
 

@@ -244,7 +244,7 @@ def _shapes(dtype, d):
 @pytest.mark.parametrize("heads,kv_heads,d,page", [(4, 2, 16, 16), (3, 3, 32, 8), (6, 1, 48, 32),
                                                    (8, 1, 64, 16), (5, 5, 80, 4), (16, 2, 128, 64),
                                                    (2, 1, 256, 16), (32, 4, 64, 16), (3, 1, 18, 16),
-                                                   (32, 1, 64, 16)])
+                                                   (32, 1, 64, 16), (8, 8, 128, 16)])
 def test_paged_attention_mixed_batch(dtype, heads, kv_heads, d, page):
     """Prompt portions beside decoded tokens, scrambled block tables, NaN in every free page."""
     g = torch.Generator().manual_seed(heads * d + page)
@@ -273,7 +273,7 @@ def test_paged_attention_mixed_batch(dtype, heads, kv_heads, d, page):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("d,page,window", [(32, 8, 24), (64, 16, 100), (48, 16, 16)])
+@pytest.mark.parametrize("d,page,window", [(32, 8, 24), (64, 16, 100), (48, 16, 16), (128, 32, 100)])
 def test_paged_attention_window(dtype, d, page, window):
     heads, kv_heads = 4, 2
     g = torch.Generator().manual_seed(window)
@@ -304,10 +304,11 @@ def test_paged_attention_window(dtype, d, page, window):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("far", [0, 15, 16, 511, 512, 1023, 1100])
-def test_paged_attention_one_far_key_stands_out(dtype, far):
+@pytest.mark.parametrize("d", [64, 128])
+def test_paged_attention_one_far_key_stands_out(dtype, far, d):
     """One key among 1101 is made to dominate one head's softmax: the output must be that key's
     value.  A wrong page, offset or tile edge would show as a different value."""
-    heads, kv_heads, d, page = 8, 2, 64, 16
+    heads, kv_heads, page = 8, 2, 16
     g = torch.Generator().manual_seed(far)
     fx = PagedFixture([1101], kv_heads, d, page, dtype, DEV, seed=far)
     q = torch.randn(1, heads, d, generator=g).to(dtype).float()

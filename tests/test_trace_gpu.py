@@ -161,6 +161,29 @@ def test_cuts_agree_with_each_other(dtype_name, model_root):
             assert_close(got, base[key], DTYPES[dtype_name], f"{schedule} against whole {key}")
 
 
+@pytest.mark.parametrize("name", ["tiny_d", "tiny_e"])
+@pytest.mark.parametrize("dtype_name", ["float32", "bfloat16"])
+@pytest.mark.parametrize("schedule", ["whole", "portions", "mixed_tight"])
+def test_replay_at_head_sizes_64_and_128(name, dtype_name, schedule, model_root):
+    """The head sizes of the full-size Llama models: in bfloat16 their prompt portions go through
+    the tensor-memory attention kernel (two row tiles a block at 64, one at 128)."""
+    from distengine_b200.engine.replay import build_runner
+    folder, config, requests, reference = _model(name, model_root)
+    dtype = DTYPES[dtype_name]
+    steps, max_tokens = _schedules(requests)[schedule]
+    runner = build_runner(folder, dtype_name, max_tokens,
+                          page_size=tiny_configs.ALL[name]["page_size"], poison_freed_pages=True)
+    with tempfile.TemporaryDirectory() as out:
+        th.replay_in_process(runner, steps, out)
+        rows = th.collect(steps, out, config["vocab_size"])
+    assert rows
+    runner.cache.check_invariants()
+    for rid in requests:
+        positions = sorted(p for r, p in rows if r == rid)
+        got = np.stack([rows[(rid, p)] for p in positions])
+        assert_close(got, reference[dtype][rid][positions], dtype, f"{name} {schedule} {rid}")
+
+
 @pytest.mark.parametrize("name", ["tiny_b", "tiny_d"])
 def test_persistent_decode_kernel_matches_plain(name, model_root):
     """The optional single-kernel decode step (csrc/decode_fused.cu): steps of single tokens go

@@ -44,7 +44,17 @@ TINY_D = dict(
     prompts=(4, 30), max_new_tokens=6, temperature=0.0,
 )
 
-ALL = {"tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C, "tiny_d": TINY_D}
+# head size 128 (the Llama-2 and Llama-3 head), three query heads on one key/value head
+TINY_E = dict(
+    config=dict(architectures=["LlamaForCausalLM"], vocab_size=270, hidden_size=136,
+                intermediate_size=232, num_hidden_layers=2, num_attention_heads=3,
+                num_key_value_heads=1, head_dim=128, rms_norm_eps=1e-5, rope_theta=500000.0,
+                max_position_embeddings=256, tie_word_embeddings=True),
+    seed=4, norm_init="uniform", page_size=32,
+    prompts=(6, 21), max_new_tokens=6, temperature=0.0,
+)
+
+ALL = {"tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C, "tiny_d": TINY_D, "tiny_e": TINY_E}
 
 
 def make_folder(name: str, root: str, dtype: str = "float32") -> str:
