@@ -22,6 +22,15 @@
 // (src/layers/activation.py:6-9, src/models/llama.py:23-27).
 //
 // Stands where the reference calls F.linear (src/layers/linear.py:19-20) on [B, 1, H] inputs.
+//
+// The RMS norm between two products of a decode layer (src/layers/layernorm.py:12-23,
+// src/models/llama.py:74-89) can ride on them instead of being a kernel of its own (`Norm` below).
+// The product before the norm adds its (bfloat16-rounded) result to the float32 residual, writes
+// residual * norm weight in bfloat16 - the norm's output but for the row's factor
+// rsqrt(mean of squares + eps) - and leaves each block's share of every row's sum of squares.  The
+// product after the norm multiplies with those rows and applies the row's factor, which is a
+// scalar that commutes with the product, to its float32 sums before anything else happens to
+// them.  All of it is float32; the shares are added in a fixed order.
 
 #include "common.cuh"
 
@@ -59,6 +68,21 @@ template <> __device__ __forceinline__ __nv_bfloat16 to_out<__nv_bfloat16>(float
     return __float2bfloat16_rn(v);
 }
 
+// What the epilogue does for the norms around a product (all pointers may be null).
+struct Norm {
+    // the norm before this product: x holds rows without their factor; row m's sum of squares is
+    // the sum of in_parts[m * in_count + p], p < in_count
+    const float* in_parts;
+    int in_count;
+    float inv_width, eps;
+    // the norm after this product: resid[m, n] += result; out[m, n] = resid[m, n] * weight[n];
+    // out_parts[m * gridDim.x + blockIdx.x] = the block's share of row m's sum of squares
+    float* resid;
+    int ld_resid;
+    const __nv_bfloat16* weight;
+    float* out_parts;
+};
+
 // blocks of k that a warp loads before it multiplies any of them: 8 to 16 loads of 16 bytes in
 // flight per thread
 __host__ __device__ constexpr int blocks_per_round(int nt, int rows, bool gated) {
@@ -72,14 +96,17 @@ __host__ __device__ constexpr int blocks_per_round(int nt, int rows, bool gated)
 // single round it would only cost registers, and with them blocks per SM).  The launch bounds keep
 // three blocks an SM for up to 8 tokens (two with PINGPONG): a decode step's products have 256 to
 // 352 blocks, which should all be resident at once.
-template <int NT, int ROWS, bool GATED, bool PINGPONG, typename OutT>
+// NORM: the epilogue takes part in the norms around the product (`Norm`).
+template <int NT, int ROWS, bool GATED, bool PINGPONG, bool NORM, typename OutT>
 __global__ void __launch_bounds__(WARPS * 32,
                                   PINGPONG ? (NT <= 2 ? 2 : 1) : (NT == 1 ? 3 : (NT == 2 ? 2 : 1)))
 linear_small_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ w,
-                    int ldw, OutT* __restrict__ out, int ldo, int m_rows, int n_out, int k_dim) {
+                    int ldw, OutT* __restrict__ out, int ldo, int m_rows, int n_out, int k_dim,
+                    const Norm norm) {
     constexpr int SETS = GATED ? 2 : 1;              // weight row sets per block
     constexpr bool UPPER = ROWS == 16;               // rows g + 8 of the tile are in use
     __shared__ float red[WARPS][SETS][16][NT * 8 + 1];
+    __shared__ float row_factor[NT * 8];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -176,6 +203,35 @@ linear_small_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfl
     pdl_trigger();
     pdl_wait();                                   // x is the previous kernel's output
 
+    // requested now, used in the epilogue: this thread's element of the residual, and the shares
+    // of the rows' sums of squares (warp w adds up rows w and w + 8, its lanes every 32nd share)
+    float resid_early = 0.0f, sq_sum[NT] = {};
+    if constexpr (NORM) {
+        if (!GATED && norm.resid != nullptr && threadIdx.x < ROWS * m_rows) {
+            const int m = threadIdx.x / ROWS, n = n0 + threadIdx.x % ROWS;
+            if (n < n_out) resid_early = norm.resid[(size_t)m * norm.ld_resid + n];
+        }
+        if (norm.in_parts != nullptr) {
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                const int m = warp + 8 * j;
+                if (m < m_rows) {
+                    const float* parts = norm.in_parts + (size_t)m * norm.in_count;
+                    for (int p0 = 0; p0 < norm.in_count; p0 += 256) {      // 8 loads in flight
+                        float v[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int p = p0 + 32 * i + lane;
+                            v[i] = p < norm.in_count ? parts[p] : 0.0f;
+                        }
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) sq_sum[j] += v[i];
+                    }
+                }
+            }
+        }
+    }
+
     // the weights of the next round are requested before this round's are multiplied, so a warp
     // always has a round of loads in flight
     constexpr int ROUND = WARPS * U;
@@ -205,18 +261,40 @@ linear_small_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfl
             red[warp][s][g + 8][j * 8 + 2 * t] = acc[s][j][2];
             red[warp][s][g + 8][j * 8 + 2 * t + 1] = acc[s][j][3];
         }
+    if constexpr (NORM) {
+        if (norm.in_parts != nullptr) {
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                float total = sq_sum[j];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+                if (lane == 0) row_factor[warp + 8 * j] = rsqrtf(total * norm.inv_width + norm.eps);
+            }
+        }
+    }
     __syncthreads();
-    for (int e = threadIdx.x; e < ROWS * m_rows; e += WARPS * 32) {
+    // every thread goes round (the shares of a row's sum of squares are added with shuffles);
+    // element e = row m of x, weight row r of the block; the ROWS lanes of a row are neighbours
+    for (int e0 = 0; e0 < ROWS * m_rows; e0 += WARPS * 32) {
+        const int e = e0 + threadIdx.x;
         const int m = e / ROWS, r = e - m * ROWS;
         const int n = n0 + r;
-        if (n >= n_out) continue;
+        const bool live = e < ROWS * m_rows && n < n_out;
         float v[SETS];
 #pragma unroll
         for (int s = 0; s < SETS; ++s) {
             float sum = 0.0f;
+            if (live) {
 #pragma unroll
-            for (int wi = 0; wi < WARPS; ++wi) sum += red[wi][s][r][m];
+                for (int wi = 0; wi < WARPS; ++wi) sum += red[wi][s][r][m];
+            }
             v[s] = sum;
+        }
+        if constexpr (NORM) {
+            if (norm.in_parts != nullptr && live) {
+#pragma unroll
+                for (int s = 0; s < SETS; ++s) v[s] *= row_factor[m];
+            }
         }
         float y = v[0];
         if constexpr (GATED) {
@@ -226,38 +304,68 @@ linear_small_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfl
             const float up = __bfloat162float(__float2bfloat16_rn(v[SETS - 1]));
             y = gate / (1.0f + expf(-gate)) * up;
         }
-        out[(size_t)m * ldo + n] = to_out<OutT>(y);
+        if constexpr (NORM && !GATED) {
+            if (norm.resid != nullptr) {
+                // the branch is rounded to bfloat16 before it joins the residual, as when it goes
+                // through memory; the sum and the squares stay float32
+                float sum = 0.0f;
+                if (live) {
+                    const float before = e0 == 0 ? resid_early
+                                                 : norm.resid[(size_t)m * norm.ld_resid + n];
+                    sum = before + __bfloat162float(__float2bfloat16_rn(y));
+                    norm.resid[(size_t)m * norm.ld_resid + n] = sum;
+                    y = sum * __bfloat162float(norm.weight[n]);
+                }
+                float sq = sum * sum;
+#pragma unroll
+                for (int o = ROWS / 2; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+                if (r == 0 && e < ROWS * m_rows)
+                    norm.out_parts[(size_t)m * gridDim.x + blockIdx.x] = sq;
+            }
+        }
+        if (live) out[(size_t)m * ldo + n] = to_out<OutT>(y);
     }
 }
 
-template <int NT, int ROWS, bool GATED, typename OutT>
+template <int NT, int ROWS, bool GATED, bool NORM, typename OutT>
 int launch(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int m_rows,
-           int n_out, int k_dim, cudaStream_t s) {
+           int n_out, int k_dim, const Norm& norm, cudaStream_t s) {
     const int grid = (n_out + ROWS - 1) / ROWS;
     // more than one round of loads per warp: the gated product has no registers for two rounds
     // with three blocks an SM
     const bool rounds = (k_dim + KB - 1) / KB > WARPS * blocks_per_round(NT, ROWS, GATED);
     if (rounds && !GATED)
-        return de_launch(linear_small_kernel<NT, ROWS, GATED, true, OutT>, dim3(grid),
+        return de_launch(linear_small_kernel<NT, ROWS, GATED, true, NORM, OutT>, dim3(grid),
                          dim3(WARPS * 32), 0, s, (const __nv_bfloat16*)x, ldx,
-                         (const __nv_bfloat16*)w, ldw, (OutT*)out, ldo, m_rows, n_out, k_dim);
-    return de_launch(linear_small_kernel<NT, ROWS, GATED, false, OutT>, dim3(grid),
+                         (const __nv_bfloat16*)w, ldw, (OutT*)out, ldo, m_rows, n_out, k_dim, norm);
+    return de_launch(linear_small_kernel<NT, ROWS, GATED, false, NORM, OutT>, dim3(grid),
                      dim3(WARPS * 32), 0, s, (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w,
-                     ldw, (OutT*)out, ldo, m_rows, n_out, k_dim);
+                     ldw, (OutT*)out, ldo, m_rows, n_out, k_dim, norm);
 }
 
-template <bool GATED, typename OutT>
+// few weight rows: blocks of 8 rows, so that there are blocks for every SM
+bool few_rows(int n_out) { return n_out < 16 * 2 * 148; }
+
+template <bool GATED, bool NORM, typename OutT>
 int pick(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int m_rows,
-         int n_out, int k_dim, cudaStream_t s) {
-    // few weight rows: blocks of 8 rows, so that there are blocks for every SM
-    const bool small = n_out < 16 * 2 * 148;
-#define GO(NT)                                                                                  \
-    return small ? launch<NT, 8, GATED, OutT>(x, ldx, w, ldw, out, ldo, m_rows, n_out, k_dim, s) \
-                 : launch<NT, 16, GATED, OutT>(x, ldx, w, ldw, out, ldo, m_rows, n_out, k_dim, s)
+         int n_out, int k_dim, const Norm& norm, cudaStream_t s) {
+#define GO(NT)                                                                                   \
+    return few_rows(n_out) ? launch<NT, 8, GATED, NORM, OutT>(x, ldx, w, ldw, out, ldo, m_rows,  \
+                                                               n_out, k_dim, norm, s)            \
+                           : launch<NT, 16, GATED, NORM, OutT>(x, ldx, w, ldw, out, ldo, m_rows, \
+                                                                n_out, k_dim, norm, s)
     if (m_rows <= 8) { GO(1); }
     if (m_rows <= 16) { GO(2); }
-    GO(4);
+    if constexpr (NORM) return -5; else { GO(4); }
 #undef GO
+}
+
+int check(int m_rows, int k_dim, int ldx, int ldw, const void* x, const void* w) {
+    if (m_rows > 32 || k_dim <= 0) return -2;
+    // 16-byte pieces: k a multiple of 8, rows that start on 16-byte boundaries
+    if (k_dim % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15))
+        return -3;
+    return 0;
 }
 
 }  // namespace
@@ -269,15 +377,51 @@ DE_EXPORT int de_linear_small(const void* x, int ldx, const void* w, int ldw, vo
                               int m_rows, int n_out, int k_dim, int out_f32, int gated,
                               void* stream) {
     if (m_rows <= 0 || n_out <= 0) return 0;
-    if (m_rows > 32 || k_dim <= 0) return -2;
-    // 16-byte pieces: k a multiple of 8, rows that start on 16-byte boundaries
-    if (k_dim % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15))
-        return -3;
+    if (int code = check(m_rows, k_dim, ldx, ldw, x, w)) return code;
     cudaStream_t s = (cudaStream_t)stream;
+    const Norm none = {};
     if (gated) {
         if (out_f32) return -4;
-        return pick<true, __nv_bfloat16>(x, ldx, w, ldw, out, ldo, m_rows, n_out, k_dim, s);
+        return pick<true, false, __nv_bfloat16>(x, ldx, w, ldw, out, ldo, m_rows, n_out, k_dim,
+                                                none, s);
     }
-    if (out_f32) return pick<false, float>(x, ldx, w, ldw, out, ldo, m_rows, n_out, k_dim, s);
-    return pick<false, __nv_bfloat16>(x, ldx, w, ldw, out, ldo, m_rows, n_out, k_dim, s);
+    if (out_f32)
+        return pick<false, false, float>(x, ldx, w, ldw, out, ldo, m_rows, n_out, k_dim, none, s);
+    return pick<false, false, __nv_bfloat16>(x, ldx, w, ldw, out, ldo, m_rows, n_out, k_dim, none, s);
+}
+
+// How many shares of a row's sum of squares a product with n_out outputs leaves (its blocks).
+DE_EXPORT int de_linear_small_parts(int n_out) {
+    return (n_out + (few_rows(n_out) ? 8 : 16) - 1) / (few_rows(n_out) ? 8 : 16);
+}
+
+// The same product (bfloat16 output, up to 16 rows) taking part in the norms around it.
+// in_parts [m_rows, in_count] (or null): x lacks the factor of the norm before the product, which
+// follows from these shares of the rows' sums of squares over `width` elements.
+// resid [m_rows, ld_resid] float32 (or null): the result joins the residual, out becomes residual *
+// norm_weight, and out_parts [m_rows, de_linear_small_parts(n_out)] receives the new shares.
+DE_EXPORT int de_linear_small_norm(const void* x, int ldx, const void* w, int ldw, void* out,
+                                   int ldo, int m_rows, int n_out, int k_dim, int gated,
+                                   const float* in_parts, int in_count, int width, float eps,
+                                   float* resid, int ld_resid, const void* norm_weight,
+                                   float* out_parts, void* stream) {
+    if (m_rows <= 0 || n_out <= 0) return 0;
+    if (int code = check(m_rows, k_dim, ldx, ldw, x, w)) return code;
+    if (m_rows > 16) return -5;
+    if (in_parts != nullptr && (in_count <= 0 || width <= 0)) return -6;
+    if (resid != nullptr && (norm_weight == nullptr || out_parts == nullptr || gated)) return -6;
+    Norm norm = {};
+    norm.in_parts = in_parts;
+    norm.in_count = in_count;
+    norm.inv_width = width > 0 ? 1.0f / (float)width : 0.0f;
+    norm.eps = eps;
+    norm.resid = resid;
+    norm.ld_resid = ld_resid;
+    norm.weight = (const __nv_bfloat16*)norm_weight;
+    norm.out_parts = out_parts;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (gated)
+        return pick<true, true, __nv_bfloat16>(x, ldx, w, ldw, out, ldo, m_rows, n_out, k_dim,
+                                               norm, s);
+    return pick<false, true, __nv_bfloat16>(x, ldx, w, ldw, out, ldo, m_rows, n_out, k_dim, norm, s);
 }

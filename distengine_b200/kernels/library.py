@@ -40,6 +40,8 @@ SIGNATURES: dict[str, dict[str, list]] = {
     "linear_small": {
         "de_linear_small_max_rows": [],
         "de_linear_small": [P, I, P, I, P, I, I, I, I, I, I, P],
+        "de_linear_small_parts": [I],
+        "de_linear_small_norm": [P, I, P, I, P, I, I, I, I, I, P, I, I, F, P, I, P, P, P],
     },
     "gemm_tcgen05": {
         "de_gemm_tcgen05": [P, I, P, I, P, I, I, I, I, I, I, P, P],

@@ -175,6 +175,59 @@ def _small_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
             and w.data_ptr() % 16 == 0)
 
 
+# The RMS norm between two weight-streaming products can ride on them (``csrc/linear_small.cu``):
+# the product before it adds to the residual and leaves residual * norm weight plus shares of the
+# rows' sums of squares, the product after it applies the rows' factors to its sums.
+# DISTENGINE_B200_NORM_RIDE=0 keeps the norm a kernel of its own (for measurements).
+NORM_RIDE = os.environ.get("DISTENGINE_B200_NORM_RIDE", "1") != "0"
+NORM_RIDE_ROWS = 16
+
+
+def norm_ride_parts(rows: int, w: torch.Tensor, dtype: torch.dtype) -> int:
+    """How many shares of every row's sum of squares a product of ``rows`` rows against ``w``
+    leaves when it does the following norm's work (``linear(..., after=)``), or 0 if such a
+    product does not go to the weight-streaming kernel.  The same condition says whether a product
+    against ``w`` can apply a preceding norm's row factors (``linear(..., before=)``)."""
+    if not (NORM_RIDE and dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and 0 < rows <= min(SMALL_ROWS, NORM_RIDE_ROWS) and w.shape[1] % 8 == 0
+            and w.is_contiguous() and w.data_ptr() % 16 == 0):
+        return 0
+    return int(library.load("linear_small").de_linear_small_parts(w.shape[0]))
+
+
+def _linear_small_norm(x, w, out, gated, before, after) -> None:
+    n_out = w.shape[0] // 2 if gated else w.shape[0]
+    _need(_small_ok(x, w) and x.shape[0] <= NORM_RIDE_ROWS and out.dtype == torch.bfloat16
+          and out.stride(1) == 1, "linear: a product that carries a norm must be one the "
+          "weight-streaming kernel takes (see norm_ride_parts)")
+    in_parts = in_count = width = 0
+    eps = 0.0
+    if before is not None:
+        parts = before.parts
+        _need(parts.dtype == torch.float32 and parts.is_contiguous()
+              and parts.shape[0] == x.shape[0], "linear: before.parts must be float32 [rows, count]")
+        in_parts, in_count, width, eps = parts.data_ptr(), parts.shape[1], before.width, before.eps
+    resid = ld_resid = weight = out_parts = 0
+    if after is not None:
+        lib_parts = norm_ride_parts(x.shape[0], w, x.dtype)
+        _need(after.resid.dtype == torch.float32 and after.resid.stride(1) == 1
+              and tuple(after.resid.shape) == tuple(out.shape)
+              and after.weight.dtype == torch.bfloat16 and after.weight.is_contiguous()
+              and after.weight.shape == (n_out,) and after.parts.dtype == torch.float32
+              and after.parts.is_contiguous()
+              and tuple(after.parts.shape) == (x.shape[0], lib_parts),
+              "linear: after needs resid float32 [rows, n], weight bfloat16 [n] and parts "
+              "float32 [rows, norm_ride_parts(...)]")
+        resid, ld_resid = after.resid.data_ptr(), after.resid.stride(0)
+        weight, out_parts = after.weight.data_ptr(), after.parts.data_ptr()
+    lib = library.load("linear_small")
+    _check(lib.de_linear_small_norm(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0),
+                                    out.data_ptr(), out.stride(0), x.shape[0], n_out, x.shape[1],
+                                    int(gated), in_parts, in_count, int(width), float(eps), resid,
+                                    ld_resid, weight, out_parts, _stream()),
+           "linear_small (with norm)")
+
+
 TCGEN05_ROWS = 1024     # from this many rows on, products go to this package's tcgen05 kernel
 _tile_fits: dict[tuple[int, int], bool] = {}
 
@@ -202,8 +255,15 @@ def _tcgen05_fits(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
 
 def linear(x: torch.Tensor, w: torch.Tensor, out: "torch.Tensor | None" = None,
            out_dtype: "torch.dtype | None" = None,
-           status: "torch.Tensor | None" = None) -> torch.Tensor:
+           status: "torch.Tensor | None" = None, before=None, after=None) -> torch.Tensor:
     """x @ w^T, float32 accumulation.
+
+    ``before`` (``.parts`` float32 [rows, count], ``.width``, ``.eps``): x is the output of an RMS
+    norm but for the rows' factors rsqrt(sum of the row's parts / width + eps), which the product
+    applies to its sums.  ``after`` (``.resid`` float32 [rows, n], ``.weight`` bfloat16 [n],
+    ``.parts`` float32 [rows, norm_ride_parts(...)]): the result is added to ``resid`` and ``out``
+    becomes resid * weight, ``parts`` the shares of the rows' sums of squares - what ``before``
+    of the next product needs.  Both only where ``norm_ride_parts`` is not 0.
 
     float32: this package's own CUDA-core kernel (true 32-bit).  bfloat16 with up to 16 rows
     (decode steps): this package's weight-streaming kernel (``csrc/linear_small.cu``).  bfloat16
@@ -218,13 +278,16 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: "torch.Tensor | None" = None,
         return out
     if x.dtype == torch.float32:
         _need(out.dtype == torch.float32, "linear: a float32 product has a float32 output")
+        _need(before is None and after is None, "linear: float32 products carry no norm")
         gemm_f32(x, w, out)
         return out
     _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16,
           "linear: operands must both be bfloat16 or both float32")
     _need(x.shape[1] == w.shape[1] and tuple(out.shape) == (x.shape[0], w.shape[0])
           and out.stride(1) == 1, "linear: shapes do not agree")
-    if _small_ok(x, w):
+    if before is not None or after is not None:
+        _linear_small_norm(x, w, out, False, before, after)
+    elif _small_ok(x, w):
         lib = library.load("linear_small")
         _check(lib.de_linear_small(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0),
                                    out.data_ptr(), out.stride(0), x.shape[0], w.shape[0],
@@ -256,7 +319,7 @@ def gated_needs_scratch(x: torch.Tensor, w_gate_up: torch.Tensor) -> bool:
 
 def linear_gated(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor,
                  scratch: "torch.Tensor | None" = None,
-                 status: "torch.Tensor | None" = None) -> torch.Tensor:
+                 status: "torch.Tensor | None" = None, before=None) -> torch.Tensor:
     """out[n, i] = silu(x . gate_i) * (x . up_i) for w_gate_up = [gate rows; up rows] of shape
     [2 inner, k].  bfloat16: one kernel whose epilogue applies the activation, the
     weight-streaming one up to 16 rows, the tcgen05 one from 1,024 rows.  float32 (or operands that are not
@@ -264,6 +327,9 @@ def linear_gated(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor,
     inner = w_gate_up.shape[0] // 2
     _need(tuple(out.shape) == (x.shape[0], inner), "linear_gated: out must be [N, inner]")
     if x.shape[0] == 0:
+        return out
+    if before is not None:          # x lacks its norm's row factors (see ``linear``)
+        _linear_small_norm(x, w_gate_up, out, True, before, None)
         return out
     if x.dtype == torch.bfloat16 and _small_ok(x, w_gate_up) and out.stride(1) == 1:
         lib = library.load("linear_small")

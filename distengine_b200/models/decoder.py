@@ -133,7 +133,13 @@ class DecoderModel:
         ops.embed_rows(ctx.token_ids, self.embedding, resid)
         stream = ResidualStream(resid)
         for index, entry in enumerate(self.plan):
-            self.blocks[entry.layer].forward(stream, ctx, caches[index])
+            # the norm and mixer that read the stream next, for blocks that hand a norm's work to
+            # the product before it
+            following = None
+            if index + 1 < len(self.plan):
+                later = self.blocks[self.plan[index + 1].layer]
+                following = (later.mixer_norm, later.mixer)
+            self.blocks[entry.layer].forward(stream, ctx, caches[index], following=following)
         rows = ctx.logit_rows
         logits = ctx.buffer("model.logits", (rows.shape[0], self.config.vocabulary),
                             torch.float32)

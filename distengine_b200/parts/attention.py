@@ -15,7 +15,7 @@ from ..config.model import PartSpec
 from ..kernels import ops
 from ..kernels.attention import AttentionLauncher
 from .base import (Mixer, PagedKVSpec, build_position_encoding, compute_matrix, register_mixer)
-from .context import CacheBinding, StepContext, StepPrep
+from .context import CacheBinding, NormAhead, StepContext, StepPrep, UnscaledRows
 
 
 class PagedAttention(Mixer):
@@ -62,13 +62,23 @@ class PagedAttention(Mixer):
     def prepare(self, prep: StepPrep) -> None:
         self.kernels.prepare(prep)
 
-    def forward(self, x: torch.Tensor, ctx: StepContext,
-                cache: "CacheBinding | None") -> torch.Tensor:
+    def takes_unscaled(self, n_rows: int) -> bool:
+        return ops.norm_ride_parts(n_rows, self.w_qkv, self.dtype) > 0
+
+    def ahead_parts(self, n_rows: int) -> int:
+        return ops.norm_ride_parts(n_rows, self.w_o, self.dtype)
+
+    def forward(self, x: "torch.Tensor | UnscaledRows", ctx: StepContext,
+                cache: "CacheBinding | None",
+                ahead: "NormAhead | None" = None) -> "torch.Tensor | None":
         if cache is None or cache.kind != "paged":
             raise ValueError("attention needs a paged key/value cache")
+        before = None
+        if isinstance(x, UnscaledRows):
+            before, x = x, x.rows
         n, d = x.shape[0], self.head_dim
         qkv = ctx.buffer("attention.qkv", (n, (self.heads + 2 * self.kv_heads) * d))
-        ops.linear(x, self.w_qkv, out=qkv, status=ctx.status)
+        ops.linear(x, self.w_qkv, out=qkv, status=ctx.status, before=before)
         self.position.apply(qkv[:, : self.heads * d].view(n, self.heads, d),
                             qkv[:, self.heads * d: (self.heads + self.kv_heads) * d]
                             .view(n, self.kv_heads, d), ctx)
@@ -83,6 +93,9 @@ class PagedAttention(Mixer):
                               self.heads, self.kv_heads, d, cache.k_pages, cache.v_pages,
                               cache.block_table, cache.writes, ctx.status)
             self.kernels.run(qkv, out, cache.k_pages, cache.v_pages, cache.block_table, ctx)
+        if ahead is not None:          # the product joins the residual and does the next norm's work
+            ops.linear(out, self.w_o, out=ahead.rows, status=ctx.status, after=ahead)
+            return None
         branch = ctx.buffer("attention.out", (n, self.width))
         ops.linear(out, self.w_o, out=branch, status=ctx.status)
         return branch

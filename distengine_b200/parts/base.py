@@ -18,7 +18,7 @@ from typing import Any, Callable
 import torch
 
 from ..config.model import PartSpec
-from .context import CacheBinding, ResidualStream, StepContext, StepPrep
+from .context import CacheBinding, NormAhead, ResidualStream, StepContext, StepPrep
 
 
 # ----------------------------------------------------------------------------- cache needs
@@ -70,6 +70,27 @@ class Norm(Part):
         rows [N, width] (or the rows picked by ``rows``) in the activation dtype."""
         raise NotImplementedError
 
+    def ahead(self, stream: ResidualStream, ctx: StepContext, count: int) -> "NormAhead | None":
+        """Optional: buffers with which the product before this norm does the norm's work
+        (``NormAhead``; ``count`` shares of a row's sum of squares), or None if this norm must
+        run itself."""
+        return None
+
+
+class NormRider:
+    """Optional abilities of a mixer or feed-forward whose first and last operations are matrix
+    products that can carry the norms around the part.  The defaults say no."""
+
+    def takes_unscaled(self, n_rows: int) -> bool:
+        """Whether ``forward`` accepts ``UnscaledRows`` in place of x for a step of n_rows."""
+        return False
+
+    def ahead_parts(self, n_rows: int) -> int:
+        """Not 0: ``forward`` accepts ``ahead=NormAhead`` - its last product then adds the
+        part's output to the residual itself, does the following norm's work and leaves this many
+        shares of each row's sum of squares; ``forward`` returns None."""
+        return 0
+
 
 class PositionEncoding(Part):
     def rotation_table(self) -> "tuple[torch.Tensor | None, int]":
@@ -83,7 +104,7 @@ class PositionEncoding(Part):
         d] in place before k is stored.  The default does nothing."""
 
 
-class Mixer(Part):
+class Mixer(Part, NormRider):
     def cache_spec(self) -> "PagedKVSpec | StateSpec | None":
         return None
 
@@ -93,7 +114,7 @@ class Mixer(Part):
         raise NotImplementedError
 
 
-class FeedForward(Part):
+class FeedForward(Part, NormRider):
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         raise NotImplementedError
 
@@ -111,8 +132,11 @@ class Block:
         return {"mixer": self.mixer, "feed_forward": self.feed_forward,
                 "mixer_norm": self.mixer_norm, "feed_forward_norm": self.feed_forward_norm}
 
-    def forward(self, stream: ResidualStream, ctx: StepContext,
-                cache: "CacheBinding | None") -> None:
+    def forward(self, stream: ResidualStream, ctx: StepContext, cache: "CacheBinding | None",
+                following: "tuple[Norm, Part] | None" = None) -> None:
+        """``following``: the norm and the part that read the stream after this block (the next
+        block's, if the model knows them), for arrangements that hand a norm's work to the
+        product before it."""
         raise NotImplementedError
 
 

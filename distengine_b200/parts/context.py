@@ -123,12 +123,43 @@ class StepContext:
         return self.workspace.get(name, shape, dtype or self.dtype, zero)
 
 
+@dataclass
+class UnscaledRows:
+    """A norm's output but for the rows' factors: ``rows`` [N, width] is residual * norm weight in
+    the activation dtype, and row m's factor is rsqrt(sum(parts[m]) / width + eps).  A factor is a
+    scalar of its row, so a matrix product may take ``rows`` as they are and apply it to its
+    float32 sums (``kernels.ops.linear(..., before=)``)."""
+    rows: torch.Tensor
+    parts: torch.Tensor                         # float32 [N, count]: shares of the sums of squares
+    width: int
+    eps: float
+
+
+@dataclass
+class NormAhead:
+    """A norm's work handed to the product that runs before it: that product adds its result to
+    ``resid`` and writes ``rows`` and ``parts`` as ``UnscaledRows`` describes them
+    (``kernels.ops.linear(..., after=)``), so the norm needs no kernel of its own."""
+    norm: Any                                   # the norm part whose work this is
+    resid: torch.Tensor                         # float32 [N, width]
+    weight: torch.Tensor                        # the norm's weight [width]
+    eps: float
+    rows: torch.Tensor                          # [N, width], activation dtype
+    parts: torch.Tensor                         # float32 [N, count]
+
+    def result(self) -> UnscaledRows:
+        return UnscaledRows(self.rows, self.parts, self.resid.shape[1], self.eps)
+
+
 class ResidualStream:
     """The residual stream in float32 and the branch output that has not been added yet.
 
     A norm folds ``pending`` into ``resid`` in the same kernel that normalises, so the sum is
-    formed in 32-bit and costs no pass over memory of its own."""
+    formed in 32-bit and costs no pass over memory of its own.  ``ahead``: the last product
+    already added its result and did the next norm's work (``NormAhead``); that norm hands out
+    its result instead of running."""
 
     def __init__(self, resid: torch.Tensor) -> None:
         self.resid = resid                      # float32 [N, width]
         self.pending: "torch.Tensor | None" = None
+        self.ahead: "NormAhead | None" = None

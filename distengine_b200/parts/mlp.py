@@ -9,7 +9,7 @@ import torch
 
 from ..kernels import ops
 from .base import FeedForward, compute_matrix, register_feed_forward
-from .context import StepContext
+from .context import NormAhead, StepContext, UnscaledRows
 
 
 class GatedMLP(FeedForward):
@@ -32,13 +32,26 @@ class GatedMLP(FeedForward):
         self.w_gate_up = compute_matrix(stacked, self.dtype, self.device)
         self.w_down = compute_matrix(tensors["down_proj.weight"], self.dtype, self.device)
 
-    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+    def takes_unscaled(self, n_rows: int) -> bool:
+        return ops.norm_ride_parts(n_rows, self.w_gate_up, self.dtype) > 0
+
+    def ahead_parts(self, n_rows: int) -> int:
+        return ops.norm_ride_parts(n_rows, self.w_down, self.dtype)
+
+    def forward(self, x: "torch.Tensor | UnscaledRows", ctx: StepContext,
+                ahead: "NormAhead | None" = None) -> "torch.Tensor | None":
+        before = None
+        if isinstance(x, UnscaledRows):
+            before, x = x, x.rows
         n = x.shape[0]
         act = ctx.buffer("mlp.act", (n, self.inner))
         scratch = None
-        if ops.gated_needs_scratch(x, self.w_gate_up):
+        if before is None and ops.gated_needs_scratch(x, self.w_gate_up):
             scratch = ctx.buffer("mlp.gate_up", (n, 2 * self.inner))
-        ops.linear_gated(x, self.w_gate_up, act, scratch, status=ctx.status)
+        ops.linear_gated(x, self.w_gate_up, act, scratch, status=ctx.status, before=before)
+        if ahead is not None:          # the product joins the residual and does the next norm's work
+            ops.linear(act, self.w_down, out=ahead.rows, status=ctx.status, after=ahead)
+            return None
         out = ctx.buffer("mlp.out", (n, self.width))
         ops.linear(act, self.w_down, out=out, status=ctx.status)
         return out

@@ -11,7 +11,7 @@ import torch
 
 from ..kernels import ops
 from .base import Norm, register_norm, stored_vector
-from .context import ResidualStream, StepContext
+from .context import NormAhead, ResidualStream, StepContext
 
 
 class RMSNorm(Norm):
@@ -26,8 +26,19 @@ class RMSNorm(Norm):
     def load(self, tensors):
         self.weight = stored_vector(tensors["weight"], self.dtype, self.device)
 
+    def ahead(self, stream: ResidualStream, ctx: StepContext, count: int):
+        if self.weight.dtype != torch.bfloat16 or stream.pending is not None:
+            return None
+        n = stream.resid.shape[0]
+        return NormAhead(self, stream.resid, self.weight, self.eps,
+                         ctx.buffer("norm.out", (n, self.width)),
+                         ctx.buffer("norm.parts", (n, count), torch.float32))
+
     def forward(self, stream: ResidualStream, ctx: StepContext, rows=None,
                 out_name: str = "norm.out") -> torch.Tensor:
+        if stream.ahead is not None:
+            raise RuntimeError("this norm's work was handed to the product before it: its "
+                               "result is stream.ahead.result()")
         n_out = stream.resid.shape[0] if rows is None else rows.shape[0]
         out = ctx.buffer(out_name, (n_out, self.width))
         ops.add_rmsnorm(stream.resid, stream.pending, self.weight, self.eps, out, rows)

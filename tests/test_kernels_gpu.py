@@ -436,6 +436,53 @@ def test_linear_gated(m, k, inner, small_rows, monkeypatch):
     assert_close(out, plain.plain_swiglu(gate, up, torch.bfloat16), torch.bfloat16, "linear_gated")
 
 
+@pytest.mark.parametrize("m", [1, 5, 8, 11, 16])
+@pytest.mark.parametrize("width,inner,eps", [(2048, 5632, 1e-5), (120, 200, 3e-6), (4096, 1024, 1e-6),
+                                             (72, 4800, 1e-5)])
+def test_norm_carried_by_the_products_around_it(m, width, inner, eps):
+    """down -> (residual sum, RMS norm) -> gate/up and -> plain product, with the norm's work done
+    by the epilogues of the products: the residual, and the outputs of the products after the
+    norm, against the plain product, sum, norm, product."""
+    from types import SimpleNamespace
+    from distengine_b200.kernels import ops as raw
+    g = torch.Generator().manual_seed(m * width + inner)
+    act = torch.randn(m, inner, generator=g).to(torch.bfloat16)
+    w_down = (torch.randn(width, inner, generator=g) * 0.05).to(torch.bfloat16)
+    resid = torch.randn(m, width, generator=g) * 3.0
+    resid[m // 2] *= 40.0                                  # rows of very different norms
+    norm_w = (1.0 + 0.5 * torch.randn(width, generator=g)).to(torch.bfloat16)
+    w_next = (torch.randn(2 * inner, width, generator=g) * 0.1).to(torch.bfloat16)
+    dev = lambda t: t.to(DEV)
+    count = raw.norm_ride_parts(m, dev(w_down), torch.bfloat16)
+    assert count > 0
+    ahead = SimpleNamespace(resid=dev(resid).clone(), weight=dev(norm_w),
+                            parts=torch.full((m, count), float("nan"), device=DEV),
+                            width=width, eps=eps)
+    rows = torch.full((m, width), float("nan"), dtype=torch.bfloat16, device=DEV)
+    raw.linear(dev(act), dev(w_down), out=rows, after=ahead)
+    # plain: product (rounded), sum in float32, norm
+    branch = plain.plain_linear(act.float(), w_down.float(), torch.bfloat16)
+    total = resid + branch
+    # (the branch is a bfloat16 value: where the kernel's float32 sum and the plain float64 sum
+    # fall on different sides of a rounding boundary the residual differs by a bfloat16 step)
+    assert_close(ahead.resid, total, torch.bfloat16, "residual sum in the epilogue")
+    squares = ahead.parts.sum(dim=1).cpu()
+    mine = ahead.resid.cpu()
+    assert torch.allclose(squares, (mine * mine).sum(dim=1), rtol=1e-5)
+    assert torch.equal(rows.cpu(), (mine * norm_w.float()).to(torch.bfloat16))
+    normed = plain.plain_rmsnorm(total, norm_w.float(), eps, torch.bfloat16)
+    out = torch.empty(m, inner, dtype=torch.bfloat16, device=DEV)
+    raw.linear_gated(rows, dev(w_next), out, before=ahead)
+    gate = plain.plain_linear(normed, w_next[:inner].float(), torch.bfloat16)
+    up = plain.plain_linear(normed, w_next[inner:].float(), torch.bfloat16)
+    assert_close(out, plain.plain_swiglu(gate, up, torch.bfloat16), torch.bfloat16,
+                 "gated product after the carried norm")
+    out = torch.empty(m, 2 * inner, dtype=torch.bfloat16, device=DEV)
+    raw.linear(rows, dev(w_next), out=out, before=ahead)
+    assert_close(out, plain.plain_linear(normed, w_next.float(), torch.bfloat16), torch.bfloat16,
+                 "product after the carried norm")
+
+
 @pytest.mark.parametrize("m,n,k", [(128, 128, 64), (77, 200, 120), (300, 384, 2048), (129, 331 + 5, 72),
                                    (2048, 256, 5632), (33, 50, 8), (2048, 2560, 136),
                                    (1500, 4100, 72), (20000, 264, 64)])
