@@ -46,11 +46,15 @@ constexpr int NT = NK / 8;
 constexpr int DT = D / 8;
 constexpr int CHUNKS = D / 8;          // 16-byte pieces of a key's row
 constexpr int MAX_CLUSTER = 8;
+#ifndef DECODE_STAGES
+#define DECODE_STAGES 2
+#endif
+constexpr int STAGES = DECODE_STAGES;  // key tiles in flight or in use
 
 // shared memory, in bytes from the start (all offsets multiples of 16)
-constexpr int OFF_K = 0;                                         // [2][KT][LDS] bf16
-constexpr int OFF_V = OFF_K + 2 * KT * LDS * 2;                  // [2][KT][LDS] bf16
-constexpr int OFF_Q = OFF_V + 2 * KT * LDS * 2;                  // [16][LDS] bf16
+constexpr int OFF_K = 0;                                         // [STAGES][KT][LDS] bf16
+constexpr int OFF_V = OFF_K + STAGES * KT * LDS * 2;             // [STAGES][KT][LDS] bf16
+constexpr int OFF_Q = OFF_V + STAGES * KT * LDS * 2;             // [16][LDS] bf16
 constexpr int OFF_KNEW = OFF_Q + ROWS * LDS * 2;                 // [LDS] bf16
 constexpr int OFF_VNEW = OFF_KNEW + LDS * 2;                     // [LDS] bf16
 constexpr int SMEM_TILES = OFF_VNEW + LDS * 2;
@@ -161,11 +165,12 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int qkv_stride,
         *reinterpret_cast<uint4*>(dst + ch * 8) = *reinterpret_cast<const uint4*>(src + ch * 8);
     };
 
-    // the first two tiles are requested before the wait (see the head of the file)
-    if (k_lo < hi) load_tile(k_lo, 0);
-    cp_async_commit();
-    if (k_lo + KT < hi) load_tile(k_lo + KT, 1);
-    cp_async_commit();
+    // the first tiles are requested before the wait (see the head of the file)
+#pragma unroll
+    for (int t = 0; t < STAGES; ++t) {
+        if (k_lo + t * KT < hi) load_tile(k_lo + t * KT, t);
+        cp_async_commit();
+    }
 
     // what does not depend on qkv: the angles' cosines and sines, the page the token's key goes to
     const int half = rot / 2;
@@ -262,8 +267,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int qkv_stride,
                         *reinterpret_cast<const uint4*>(v_new + ch * 8);
             }
         }
-        fill_new(k_lo, 0);
-        fill_new(k_lo + KT, 1);
+#pragma unroll
+        for (int t = 0; t < STAGES; ++t) fill_new(k_lo + t * KT, t);
         STAMP(3);
 
         unsigned qf[D / 16][4];
@@ -277,8 +282,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int qkv_stride,
             }
 
         int stage = 0;
-        for (int kt = k_lo; kt < hi; kt += KT, stage ^= 1) {
-            cp_async_wait<1>();                       // this tile has landed; the next may be on its way
+        for (int kt = k_lo; kt < hi; kt += KT, stage = stage + 1 == STAGES ? 0 : stage + 1) {
+            cp_async_wait<STAGES - 1>();              // this tile has landed; the next may be on their way
             __syncthreads();
 
             const __nv_bfloat16* kb = k_s + stage * KT * LDS + wn * NK * LDS;
@@ -360,9 +365,9 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int qkv_stride,
                 }
             }
             __syncthreads();                   // this stage is free: the tile after the next goes there
-            if (kt + 2 * KT < hi) {
-                load_tile(kt + 2 * KT, stage);
-                fill_new(kt + 2 * KT, stage);
+            if (kt + STAGES * KT < hi) {
+                load_tile(kt + STAGES * KT, stage);
+                fill_new(kt + STAGES * KT, stage);
             }
             cp_async_commit();
         }
@@ -580,6 +585,24 @@ DE_EXPORT int de_attn_decode(const void* qkv, int qkv_stride, void* out, int out
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
     }
+    // the step's common split of an SM's memory, unless this launch needs more blocks an SM than
+    // that leaves room for (then the driver's choice for this kernel)
+    static int sms = 0;
+    if (sms == 0) {
+        int device = 0;
+        cudaGetDevice(&device);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    }
+    const long long blocks = (long long)num_items * kv_heads;
+    // (the split is rounded up to one of these sizes; a block takes 1 KB beside its own)
+    const int sizes_kb[] = {8, 16, 32, 64, 100, 132, 164, 196, 228};
+    int split_kb = 228;
+    for (int i = 8; i >= 0; --i)
+        if (sizes_kb[i] * 100 >= g_carveout * 228) split_kb = sizes_kb[i];
+    const long long room = g_carveout < 0 ? 0 : (long long)split_kb * 1024 / (SMEM_BYTES + 1024);
+    // (one block an SM fewer than fit: clusters need their blocks placed together, and a launch
+    // that fills every place waits for places; measured at batch 12, 384 blocks of 444 places)
+    de_prefer_carveout(attn_decode_kernel, blocks <= (room - 1) * sms ? g_carveout : -1);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)num_items * (unsigned)kv_heads);
     cfg.blockDim = dim3(THREADS);

@@ -85,9 +85,38 @@ __device__ __forceinline__ void rope_rotate(float a, float b, float c, float s, 
 
 static int g_pdl = 1;          // per library; de_set_pdl switches it
 
+// How an SM's memory is split into shared memory and L1 is a preference of each kernel, and an SM
+// cannot hold blocks of two kernels that want different splits: the second kernel's blocks wait
+// until the first's are gone, which takes away the overlap that programmatic dependent launch
+// gives.  The kernels of a decode step therefore all ask for the same split, `g_carveout` percent
+// of the memory as shared memory (-1: the driver's choice per kernel); de_set_carveout sets it
+// per library.  Measured on B200, TinyLlama shape, batch 8: 0.785 ms a step at 45-55 percent
+// (132 KB shared memory) against 0.815 with the driver's choices, 0.86 at 35-40, 0.96 at 75,
+// 1.18 at 100 (the products' token rows no longer fit in L1).
+static int g_carveout = -1;
+
+template <typename F>
+static inline void de_prefer_carveout(F kernel, int percent) {
+    static const void* seen[64];
+    static int value[64];
+    static int count = 0;
+    int at = 0;
+    while (at < count && seen[at] != (const void*)kernel) ++at;
+    if (at == count) {
+        if (count == 64) return;
+        seen[count] = (const void*)kernel;
+        value[count++] = -1;
+    }
+    if (value[at] == percent) return;
+    cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                         percent < 0 ? (int)cudaSharedmemCarveoutDefault : percent);
+    value[at] = percent;
+}
+
 template <typename... KArgs, typename... Args>
 static inline int de_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
                             cudaStream_t stream, Args... args) {
+    de_prefer_carveout(kernel, g_carveout);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -101,5 +130,9 @@ static inline int de_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, siz
     return de_check(cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...));
 }
 
-#define DE_DEFINE_PDL_SWITCH \
-    DE_EXPORT int de_set_pdl(int on) { g_pdl = on ? 1 : 0; return 0; }
+#define DE_DEFINE_PDL_SWITCH                                               \
+    DE_EXPORT int de_set_pdl(int on) { g_pdl = on ? 1 : 0; return 0; }     \
+    DE_EXPORT int de_set_carveout(int percent) {                           \
+        g_carveout = percent < 0 ? -1 : (percent > 100 ? 100 : percent);   \
+        return 0;                                                          \
+    }

@@ -81,7 +81,9 @@ def choose_decode_split(num_tiles: int, kv_heads: int, span: int,
     tiles_of_keys = max((span + 63) // 64, 1)
     cluster = 1
     # about four blocks an SM at most, and no block without a whole tile of 64 keys
-    while (cluster < max_cluster and blocks * cluster * 2 <= 4 * SM_COUNT
+    import os
+    per_sm = int(os.environ.get("DISTENGINE_B200_DECODE_BLOCKS_PER_SM", "4"))
+    while (cluster < max_cluster and blocks * cluster * 2 <= per_sm * SM_COUNT
            and cluster * 2 <= tiles_of_keys):
         cluster *= 2
     clusters = (span + cluster * 2048 - 1) // (cluster * 2048)          # 2048 keys a block at most

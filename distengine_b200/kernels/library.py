@@ -69,6 +69,11 @@ SIGNATURES: dict[str, dict[str, list]] = {
 
 _loaded: dict[tuple[str, tuple[str, ...]], ctypes.CDLL] = {}
 
+# percent of an SM's memory that the decode step's kernels ask for as shared memory (-1: each
+# kernel's default)
+CARVEOUT = int(os.environ.get("DISTENGINE_B200_CARVEOUT", "50"))
+CARVEOUT_MODULES = ("core", "linear_small", "attention_decode")
+
 
 def default_build_requests() -> list[tuple[str, tuple[str, ...]]]:
     """Every module; the per-head-size attention for the head sizes of common models."""
@@ -103,6 +108,11 @@ def load(module: str, defines: tuple[str, ...] = ()) -> ctypes.CDLL:
     lib.de_set_pdl.argtypes = [c_int]
     lib.de_set_pdl.restype = c_int
     lib.de_set_pdl(0 if os.environ.get("DISTENGINE_B200_PDL", "1") == "0" else 1)
+    # the kernels of a decode step ask for one split of an SM's memory (see csrc/common.cuh)
+    if module in CARVEOUT_MODULES:
+        lib.de_set_carveout.argtypes = [c_int]
+        lib.de_set_carveout.restype = c_int
+        lib.de_set_carveout(CARVEOUT)
     _loaded[key] = lib
     return lib
 
