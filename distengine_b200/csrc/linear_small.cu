@@ -333,7 +333,10 @@ int launch(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, i
     const int grid = (n_out + ROWS - 1) / ROWS;
     // more than one round of loads per warp: the gated product has no registers for two rounds
     // with three blocks an SM
-    const bool rounds = (k_dim + KB - 1) / KB > WARPS * blocks_per_round(NT, ROWS, GATED);
+    bool rounds = (k_dim + KB - 1) / KB > WARPS * blocks_per_round(NT, ROWS, GATED);
+#ifdef LINEAR_SMALL_NO_PINGPONG
+    rounds = false;
+#endif
     if (rounds && !GATED)
         return de_launch(linear_small_kernel<NT, ROWS, GATED, true, NORM, OutT>, dim3(grid),
                          dim3(WARPS * 32), 0, s, (const __nv_bfloat16*)x, ldx,
