@@ -81,9 +81,10 @@ def default_build_requests() -> list[tuple[str, tuple[str, ...]]]:
                 if module in SIGNATURES
                 and module not in ("attention_mma", "attention_decode", "decode_fused",
                                    "attention_tcgen05")]
-    return (requests + [("attention_mma", (f"HEAD_DIM={d}",)) for d in (64, 128)]
+    # (16: the head size of the tiny model that the smoke test generates with)
+    return (requests + [("attention_mma", (f"HEAD_DIM={d}",)) for d in (16, 64, 128)]
             + [("attention_tcgen05", (f"HEAD_DIM={d}",)) for d in (64, 128)]
-            + [("attention_decode", (f"HEAD_DIM={d}",)) for d in (64, 128)]
+            + [("attention_decode", (f"HEAD_DIM={d}",)) for d in (16, 64, 128)]
             + [("decode_fused", (f"HEAD_DIM={d}",)) for d in (64, 128)])
 
 
