@@ -99,7 +99,7 @@ __host__ __device__ constexpr int blocks_per_round(int nt, int rows, bool gated)
 // NORM: the epilogue takes part in the norms around the product (`Norm`).
 template <int NT, int ROWS, bool GATED, bool PINGPONG, bool NORM, typename OutT>
 __global__ void __launch_bounds__(WARPS * 32,
-                                  PINGPONG ? (NT <= 2 ? 2 : 1) : (NT == 1 ? 3 : (NT == 2 ? 2 : 1)))
+                                  PINGPONG ? (NT <= 2 ? 2 : 1) : (NT <= 2 ? 3 : 1))
 linear_small_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ w,
                     int ldw, OutT* __restrict__ out, int ldo, int m_rows, int n_out, int k_dim,
                     const Norm norm) {
