@@ -43,6 +43,10 @@ SIGNATURES: dict[str, dict[str, list]] = {
         "de_linear_small_parts": [I],
         "de_linear_small_norm": [P, I, P, I, P, I, I, I, I, I, P, I, I, F, P, I, P, P, P],
     },
+    "linear_mid": {
+        "de_linear_mid_max_rows": [], "de_linear_mid_parts": [I],
+        "de_linear_mid": [P, I, P, I, P, I, I, I, I, I, I, P, I, I, F, P, I, P, P, I, P, P],
+    },
     "gemm_tcgen05": {
         "de_gemm_tcgen05": [P, I, P, I, P, I, I, I, I, I, I, P, P],
         "de_gemm_tcgen05_tile": [I, I, I], "de_gemm_tcgen05_sms": [],

@@ -183,19 +183,75 @@ NORM_RIDE = os.environ.get("DISTENGINE_B200_NORM_RIDE", "1") != "0"
 NORM_RIDE_ROWS = 16
 
 
+# From SMALL_ROWS + 1 to this many tokens a product goes to the swapped-operand tcgen05 kernel
+# (``csrc/linear_mid.cu``, which takes up to 128); DISTENGINE_B200_MID_ROWS=0 gives those to the
+# library product.  Measured on B200 in decode steps (TinyLlama shape, a step in ms, this kernel
+# against the library product with separate norm and activation kernels): batch 20 1.12 / 1.16,
+# batch 32 1.18 / 1.20, batch 48 1.36 / 1.28, batch 64 1.42 / 1.33.
+MID_ROWS = int(os.environ.get("DISTENGINE_B200_MID_ROWS", "32"))
+
+
+def _mid_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return (SMALL_ROWS < x.shape[0] <= MID_ROWS and x.shape[1] % 8 == 0 and x.stride(1) == 1
+            and w.is_contiguous() and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+            and w.data_ptr() % 16 == 0)
+
+
+def _linear_mid(x, w, out, gated, before, after, status) -> None:
+    global _tcgen05_status
+    n_out = w.shape[0] // 2 if gated else w.shape[0]
+    _need(out.dtype in (torch.bfloat16, torch.float32) and out.stride(1) == 1
+          and tuple(out.shape) == (x.shape[0], n_out), "linear_mid: out [tokens, n]")
+    if status is None:
+        if _tcgen05_status is None or _tcgen05_status.device != x.device:
+            _tcgen05_status = torch.zeros(1, dtype=torch.int32, device=x.device)
+        status = _tcgen05_status
+    in_parts = in_count = width = 0
+    eps = 0.0
+    if before is not None:
+        parts = before.parts
+        _need(parts.dtype == torch.float32 and parts.is_contiguous()
+              and parts.shape[0] == x.shape[0], "linear: before.parts must be float32 [rows, count]")
+        in_parts, in_count, width, eps = parts.data_ptr(), parts.shape[1], before.width, before.eps
+    resid = ld_resid = weight = out_parts = 0
+    lib = library.load("linear_mid")
+    if after is not None:
+        _need(after.resid.dtype == torch.float32 and after.resid.stride(1) == 1
+              and tuple(after.resid.shape) == tuple(out.shape) and out.dtype == torch.bfloat16
+              and after.weight.dtype == torch.bfloat16 and after.weight.is_contiguous()
+              and after.weight.shape == (n_out,) and after.parts.dtype == torch.float32
+              and after.parts.is_contiguous()
+              and tuple(after.parts.shape) == (x.shape[0], lib.de_linear_mid_parts(n_out)),
+              "linear: after needs resid float32 [rows, n], weight bfloat16 [n] and parts "
+              "float32 [rows, norm_ride_parts(...)]")
+        resid, ld_resid = after.resid.data_ptr(), after.resid.stride(0)
+        weight, out_parts = after.weight.data_ptr(), after.parts.data_ptr()
+    _check(lib.de_linear_mid(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(),
+                             out.stride(0), x.shape[0], n_out, x.shape[1],
+                             int(out.dtype == torch.float32), int(gated), in_parts, in_count,
+                             int(width), float(eps), resid, ld_resid, weight, out_parts, 0,
+                             status.data_ptr(), _stream()), "linear_mid")
+
+
 def norm_ride_parts(rows: int, w: torch.Tensor, dtype: torch.dtype) -> int:
     """How many shares of every row's sum of squares a product of ``rows`` rows against ``w``
     leaves when it does the following norm's work (``linear(..., after=)``), or 0 if such a
     product does not go to the weight-streaming kernel.  The same condition says whether a product
     against ``w`` can apply a preceding norm's row factors (``linear(..., before=)``)."""
     if not (NORM_RIDE and dtype == torch.bfloat16 and w.dtype == torch.bfloat16
-            and 0 < rows <= min(SMALL_ROWS, NORM_RIDE_ROWS) and w.shape[1] % 8 == 0
-            and w.is_contiguous() and w.data_ptr() % 16 == 0):
+            and w.shape[1] % 8 == 0 and w.is_contiguous() and w.data_ptr() % 16 == 0):
         return 0
-    return int(library.load("linear_small").de_linear_small_parts(w.shape[0]))
+    if 0 < rows <= min(SMALL_ROWS, NORM_RIDE_ROWS):
+        return int(library.load("linear_small").de_linear_small_parts(w.shape[0]))
+    if SMALL_ROWS < rows <= MID_ROWS:
+        return int(library.load("linear_mid").de_linear_mid_parts(w.shape[0]))
+    return 0
 
 
-def _linear_small_norm(x, w, out, gated, before, after) -> None:
+def _linear_small_norm(x, w, out, gated, before, after, status=None) -> None:
+    if _mid_ok(x, w):
+        _linear_mid(x, w, out, gated, before, after, status)
+        return
     n_out = w.shape[0] // 2 if gated else w.shape[0]
     _need(_small_ok(x, w) and x.shape[0] <= NORM_RIDE_ROWS and out.dtype == torch.bfloat16
           and out.stride(1) == 1, "linear: a product that carries a norm must be one the "
@@ -286,7 +342,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: "torch.Tensor | None" = None,
     _need(x.shape[1] == w.shape[1] and tuple(out.shape) == (x.shape[0], w.shape[0])
           and out.stride(1) == 1, "linear: shapes do not agree")
     if before is not None or after is not None:
-        _linear_small_norm(x, w, out, False, before, after)
+        _linear_small_norm(x, w, out, False, before, after, status)
+    elif _mid_ok(x, w):
+        _linear_mid(x, w, out, False, None, None, status)
     elif _small_ok(x, w):
         lib = library.load("linear_small")
         _check(lib.de_linear_small(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0),
@@ -309,7 +367,7 @@ def gated_needs_scratch(x: torch.Tensor, w_gate_up: torch.Tensor) -> bool:
     the activation kernel is faster)."""
     if x.dtype != torch.bfloat16 or w_gate_up.dtype != torch.bfloat16:
         return True
-    if _small_ok(x, w_gate_up):
+    if _small_ok(x, w_gate_up) or _mid_ok(x, w_gate_up):
         return False
     return not (x.shape[0] >= TCGEN05_ROWS and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0
                 and w_gate_up.stride(0) % 8 == 0 and x.stride(1) == 1
@@ -329,7 +387,11 @@ def linear_gated(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor,
     if x.shape[0] == 0:
         return out
     if before is not None:          # x lacks its norm's row factors (see ``linear``)
-        _linear_small_norm(x, w_gate_up, out, True, before, None)
+        _linear_small_norm(x, w_gate_up, out, True, before, None, status)
+        return out
+    if (x.dtype == torch.bfloat16 and _mid_ok(x, w_gate_up) and out.stride(1) == 1
+            and out.dtype == torch.bfloat16):
+        _linear_mid(x, w_gate_up, out, True, None, None, status)
         return out
     if x.dtype == torch.bfloat16 and _small_ok(x, w_gate_up) and out.stride(1) == 1:
         lib = library.load("linear_small")

@@ -436,15 +436,60 @@ def test_linear_gated(m, k, inner, small_rows, monkeypatch):
     assert_close(out, plain.plain_swiglu(gate, up, torch.bfloat16), torch.bfloat16, "linear_gated")
 
 
-@pytest.mark.parametrize("m", [1, 5, 8, 11, 16])
+@pytest.mark.parametrize("m", [17, 32, 50, 64, 100, 128])
+@pytest.mark.parametrize("k,n", [(64, 50), (2048, 2560), (120, 331), (5632, 2048), (200, 8),
+                                 (2048, 4100)])
+def test_linear_mid(m, k, n, monkeypatch):
+    """The swapped-operand tcgen05 product for 17 to 128 tokens (all token counts the kernel takes,
+    also those that the engine gives to the library product): bfloat16 and float32 output, the
+    split of k chosen by the kernel and every split forced, the gated epilogue."""
+    from distengine_b200.kernels import library
+    from distengine_b200.kernels import ops as raw
+    monkeypatch.setattr(raw, "MID_ROWS", 128)
+    g = torch.Generator().manual_seed(m * k + n)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(n, k, generator=g) * 0.1).to(torch.bfloat16)
+    dx, dw = x.to(DEV), w.to(DEV)
+    assert raw._mid_ok(dx, dw)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    want = plain.plain_linear(x.float(), w.float(), torch.bfloat16)
+    got = raw.linear(dx, dw, status=status)
+    assert status.item() == 0
+    assert_close(got, want, torch.bfloat16, "linear_mid")
+    wide = raw.linear(dx, dw, out_dtype=torch.float32, status=status)
+    assert_close(wide, plain.plain_linear(x.float(), w.float(), torch.bfloat16, keep_f32=True),
+                 torch.float32, "linear_mid -> f32")
+    lib = library.load("linear_mid")
+    for split in (1, 2, 4, 8):
+        out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+        code = lib.de_linear_mid(dx.data_ptr(), dx.stride(0), dw.data_ptr(), dw.stride(0),
+                                 out.data_ptr(), out.stride(0), m, n, k, 0, 0, 0, 0, 0, 0.0, 0, 0,
+                                 0, 0, split, status.data_ptr(),
+                                 torch.cuda.current_stream().cuda_stream)
+        assert code == 0 and status.item() == 0
+        assert_close(out, want, torch.bfloat16, f"linear_mid split {split}")
+    if n % 2 == 0:
+        inner = n // 2
+        out = torch.empty(m, inner, dtype=torch.bfloat16, device=DEV)
+        raw.linear_gated(dx, dw, out, status=status)
+        assert status.item() == 0
+        gate = plain.plain_linear(x.float(), w[:inner].float(), torch.bfloat16)
+        up = plain.plain_linear(x.float(), w[inner:].float(), torch.bfloat16)
+        assert_close(out, plain.plain_swiglu(gate, up, torch.bfloat16), torch.bfloat16,
+                     "linear_mid gated")
+
+
+@pytest.mark.parametrize("m", [1, 5, 8, 11, 16, 17, 40, 64, 128])
 @pytest.mark.parametrize("width,inner,eps", [(2048, 5632, 1e-5), (120, 200, 3e-6), (4096, 1024, 1e-6),
                                              (72, 4800, 1e-5)])
-def test_norm_carried_by_the_products_around_it(m, width, inner, eps):
+def test_norm_carried_by_the_products_around_it(m, width, inner, eps, monkeypatch):
     """down -> (residual sum, RMS norm) -> gate/up and -> plain product, with the norm's work done
     by the epilogues of the products: the residual, and the outputs of the products after the
-    norm, against the plain product, sum, norm, product."""
+    norm, against the plain product, sum, norm, product.  Up to 16 tokens in the weight-streaming
+    kernel, more in the swapped-operand tcgen05 kernel."""
     from types import SimpleNamespace
     from distengine_b200.kernels import ops as raw
+    monkeypatch.setattr(raw, "MID_ROWS", 128)
     g = torch.Generator().manual_seed(m * width + inner)
     act = torch.randn(m, inner, generator=g).to(torch.bfloat16)
     w_down = (torch.randn(width, inner, generator=g) * 0.05).to(torch.bfloat16)
