@@ -184,6 +184,44 @@ def test_replay_at_head_sizes_64_and_128(name, dtype_name, schedule, model_root)
         assert_close(got, reference[dtype][rid][positions], dtype, f"{name} {schedule} {rid}")
 
 
+WIDE = dict(architectures=["LlamaForCausalLM"], vocab_size=203, hidden_size=2048,
+            intermediate_size=1024, num_hidden_layers=2, num_attention_heads=32,
+            num_key_value_heads=4, rms_norm_eps=1e-5, rope_theta=10000.0,
+            max_position_embeddings=4096, tie_word_embeddings=False)
+
+
+def test_a_prompt_of_2048_tokens_at_full_width():
+    """Layers as wide as the benchmark's, two of them, a prompt of 2,100 tokens fed whole and
+    then cut in two ways, then eight tokens one by one: the portions' products are the tcgen05
+    kernels at the sizes they were made for, the single tokens' the weight-streaming ones with
+    the norms in their epilogues; logits against the plain implementation at a few positions."""
+    from distengine_b200.engine.replay import build_runner
+    from distengine_b200.weights import write_random_model
+    with tempfile.TemporaryDirectory() as root:
+        folder = write_random_model(WIDE, f"{root}/wide", seed=5, norm_init="uniform")
+        config, weights = plain.load_model_folder(folder)
+        rng = np.random.default_rng(4)
+        ids = [int(t) for t in rng.integers(0, 203, size=2108)]
+        want = plain.plain_forward(config, weights, ids, torch.bfloat16).numpy()
+        places = [0, 1, 777, 2047, 2048, 2099] + list(range(2100, 2108))
+        for cuts in ([2100], [2048, 52], [1030, 1070]):
+            cuts = cuts + [1] * 8
+            runner = build_runner(folder, "bfloat16", 2176, page_size=64)
+            steps, at = [], 0
+            for size in cuts:
+                asked = [p - at for p in places if at <= p < at + size]
+                steps.append({"step": len(steps), "entries": [
+                    {"id": "w", "tokens": ids[at: at + size], "want": asked}], "end": []})
+                at += size
+            with tempfile.TemporaryDirectory() as out:
+                th.replay_in_process(runner, steps, out)
+                rows = th.collect(steps, out, 203)
+            assert sorted(p for _, p in rows) == places
+            for (_, pos), got in rows.items():
+                assert_close(got, want[pos], torch.bfloat16,
+                             f"wide model, cuts {cuts[:2]}, position {pos}")
+
+
 @pytest.mark.parametrize("name", ["tiny_b", "tiny_d"])
 def test_persistent_decode_kernel_matches_plain(name, model_root):
     """The optional single-kernel decode step (csrc/decode_fused.cu): steps of single tokens go
