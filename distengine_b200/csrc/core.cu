@@ -475,7 +475,8 @@ __device__ __forceinline__ float uniform_of(unsigned long long base, int i) {
     return ((float)(z >> 41) + 0.5f) * (1.0f / 8388608.0f);     // 23 bits + 0.5: exact, in (0,1)
 }
 
-__global__ void sample_rows_kernel(const float* __restrict__ logits, int vocab,
+__global__ void __launch_bounds__(1024)
+sample_rows_kernel(const float* __restrict__ logits, int vocab,
                                    const float* __restrict__ temperature,
                                    const long long* __restrict__ seed,
                                    const int* __restrict__ position, int* __restrict__ out) {
@@ -492,10 +493,32 @@ __global__ void sample_rows_kernel(const float* __restrict__ logits, int vocab,
                (unsigned long long)(long long)position[r] * 0xD1B54A32D192ED03ull;
     float bv = -INFINITY;
     int bi = 0x7fffffff;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        float v = row[i];
+    auto take = [&](float v, int i) {
         if (t > 0.0f) v = v / t - logf(-logf(uniform_of(base, i)));
         if (v > bv || (v == bv && i < bi) || bi == 0x7fffffff) { bv = v; bi = i; }
+    };
+    if ((vocab & 3) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0) {
+        // 16-byte loads, eight of them requested before the first is looked at
+        const float4* row4 = reinterpret_cast<const float4*>(row);
+        const int quads = vocab >> 2;
+        for (int q0 = threadIdx.x; q0 < quads; q0 += 8 * blockDim.x) {
+            float4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int q = q0 + u * blockDim.x;
+                v[u] = q < quads ? row4[q] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int q = q0 + u * blockDim.x;
+                if (q < quads) {
+                    take(v[u].x, 4 * q); take(v[u].y, 4 * q + 1);
+                    take(v[u].z, 4 * q + 2); take(v[u].w, 4 * q + 3);
+                }
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < vocab; i += blockDim.x) take(row[i], i);
     }
     // reduce (value, lowest index on ties) over the block
 #pragma unroll

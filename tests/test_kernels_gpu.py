@@ -181,24 +181,28 @@ def test_linear_bf16(n, k, m):
                  torch.float32, "linear bf16 -> f32")
 
 
-def test_sample_rows_greedy_and_ties():
+@pytest.mark.parametrize("vocab", [32003, 32000, 40004, 64])
+def test_sample_rows_greedy_and_ties(vocab):
+    """(vocabularies that are and are not multiples of four: 16-byte and single loads)"""
     ops = _ops()
     g = torch.Generator().manual_seed(0)
-    logits = torch.randn(9, 32003, generator=g)
-    logits[3, 100] = logits[3, 31000] = 50.0             # a tie: the lowest id wins
-    logits[4, 32002] = 60.0                              # the last id
+    logits = torch.randn(9, vocab, generator=g)
+    far = vocab - vocab // 30
+    logits[3, vocab // 300] = logits[3, far] = 50.0      # a tie: the lowest id wins
+    logits[4, vocab - 1] = 60.0                          # the last id
     logits[5, 0] = 60.0
+    logits[6, far] = logits[6, far + 1] = 55.0           # a tie inside one 16-byte piece
     out = torch.empty(9, dtype=torch.int32, device=DEV)
     ops.sample_rows(logits.to(DEV), out)
     want = [plain.plain_greedy(row) for row in logits]
     assert out.cpu().tolist() == want
-    assert want[3] == 100 and want[4] == 32002 and want[5] == 0
+    assert want[3] == vocab // 300 and want[4] == vocab - 1 and want[5] == 0 and want[6] == far
 
 
-def test_sample_rows_temperature_matches_plain_and_softmax():
+@pytest.mark.parametrize("vocab", [331, 332])
+def test_sample_rows_temperature_matches_plain_and_softmax(vocab):
     ops = _ops()
     g = torch.Generator().manual_seed(5)
-    vocab = 331
     logits = torch.randn(6, vocab, generator=g) * 2
     temperature = torch.tensor([0.8, 0.0, 1.5, 0.8, 0.3, 1.0])
     seed = torch.tensor([7, 7, 123456789012, 8, 7, -3], dtype=torch.int64)
