@@ -137,23 +137,25 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int qkv_stride,
 
     const size_t slab = (size_t)page * D;
     // keys and values of a tile from the cache; the token's own row is left out (fill_new)
+    // (a thread takes half a key's row: one look into the block table for its pieces)
+    static_assert(THREADS == 2 * KT && CHUNKS % 2 == 0, "two threads a key row");
     auto load_tile = [&](int kt, int stage) {
         __nv_bfloat16* kd = k_s + stage * KT * LDS;
         __nv_bfloat16* vd = v_s + stage * KT * LDS;
-        for (int c = threadIdx.x; c < KT * CHUNKS; c += THREADS) {
-            const int j = c / CHUNKS, ch = c - j * CHUNKS;
-            const int kpos = kt + j;
-            if (new_key && kpos == pos) continue;
-            bool ok = kpos >= lo && kpos < hi;
-            size_t off = 0;
-            if (ok) {
-                const int page_id = block_table[(size_t)slot * table_stride + kpos / page];
-                ok = page_id >= 0 && page_id < num_pages;
-                if (ok) off = ((size_t)page_id * kv_heads + hk) * slab + (size_t)(kpos % page) * D +
-                              ch * 8;
-            }
-            cp_async16(kd + j * LDS + ch * 8, k_pages + off, ok);
-            cp_async16(vd + j * LDS + ch * 8, v_pages + off, ok);
+        const int j = threadIdx.x >> 1, ch0 = (threadIdx.x & 1) * (CHUNKS / 2);
+        const int kpos = kt + j;
+        if (new_key && kpos == pos) return;
+        bool ok = kpos >= lo && kpos < hi;
+        size_t off = 0;
+        if (ok) {
+            const int page_id = block_table[(size_t)slot * table_stride + kpos / page];
+            ok = page_id >= 0 && page_id < num_pages;
+            if (ok) off = ((size_t)page_id * kv_heads + hk) * slab + (size_t)(kpos % page) * D;
+        }
+#pragma unroll
+        for (int ch = ch0; ch < ch0 + CHUNKS / 2; ++ch) {
+            cp_async16(kd + j * LDS + ch * 8, k_pages + off + (ok ? ch * 8 : 0), ok);
+            cp_async16(vd + j * LDS + ch * 8, v_pages + off + (ok ? ch * 8 : 0), ok);
         }
     };
     // the token's own key and value, from this launch and not from the cache, into their row
@@ -176,16 +178,13 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int qkv_stride,
     const int half = rot / 2;
     constexpr int TODO = (ROWS + 1) * (D / 2);            // pairs of 16 q rows and of the key
     constexpr int PER = (TODO + THREADS - 1) / THREADS;
-    float cs[PER], sn[PER];
-#pragma unroll
-    for (int u = 0; u < PER; ++u) {
-        const int idx = threadIdx.x + u * THREADS;
-        const int r = idx / (D / 2), j = idx - r * (D / 2);
-        const bool rotated = !empty && j < half && inv_freq != nullptr &&
-                             (r < n_rows || (r == ROWS && new_key));
+    // every row is the same token, so the angles depend on the pair's index alone
+    __shared__ float cos_s[D / 2], sin_s[D / 2];
+    for (int j = threadIdx.x; j < D / 2; j += THREADS) {
+        const bool rotated = !empty && j < half && inv_freq != nullptr;
         const float angle = rotated ? (float)pos * inv_freq[j] : 0.0f;
-        cs[u] = cosf(angle);
-        sn[u] = sinf(angle);
+        cos_s[j] = cosf(angle);
+        sin_s[j] = sinf(angle);
     }
     int write_page = -1;
     if (new_key && it.row0 == 0 && threadIdx.x < 2 * CHUNKS)
@@ -193,6 +192,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int qkv_stride,
 
     STAMP(1);
     pdl_wait();                                       // qkv is the previous kernel's output
+    __syncthreads();                                  // the cosines and sines are in place
     STAMP(2);
 
     float o_acc[DT][4];
@@ -234,8 +234,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int qkv_stride,
                 const int c1 = j < half ? j + half : c0 + 1;
                 if (j < half && inv_freq && (r < n_rows || r == ROWS)) {
                     float ra, rb;
-                    rope_rotate(__bfloat162float(a[u]), __bfloat162float(bb[u]), cs[u], sn[u], ra,
-                                rb);
+                    rope_rotate(__bfloat162float(a[u]), __bfloat162float(bb[u]), cos_s[j], sin_s[j],
+                                ra, rb);
                     dst[c0] = __float2bfloat16_rn(ra);
                     dst[c1] = __float2bfloat16_rn(rb);
                 } else {                              // unrotated features; zeros beyond the group
