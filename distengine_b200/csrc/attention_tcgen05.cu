@@ -26,7 +26,8 @@
 // results in the layout `de_attn_combine` merges.
 //
 // Every mbarrier wait is bounded (status 3, the block then runs to its end and frees its tensor
-// memory); no cluster launch, no multicast.  One block per SM (193 KB of shared memory).
+// memory); no cluster launch, every block fetches its own tiles.  One block per SM (193 KB of
+// shared memory).
 
 #include <cuda.h>
 

@@ -16,7 +16,7 @@
 //     two halves of the accumulator (src/layers/activation.py:6-9), so the activation costs no
 //     pass over memory and the product's [gate | up] output is never written.
 // Tiles are numbered with the rows of x fastest, so the blocks at work share a few tiles of w.
-// No cluster launch, no multicast; every block fetches its own tiles.
+// No cluster launch; every block fetches its own tiles.
 //
 // Every wait on an mbarrier is bounded: after SPIN_LIMIT polls a thread records status 3, stops
 // waiting, and the block runs to its end (tensor memory is freed on every path); the host raises.
