@@ -65,6 +65,21 @@ def test_greedy_generation_through_the_entry_point(name, dtype, model_root):
     assert engine.cache.num_free_pages() == engine.cache.num_pages and not engine.has_pending()
 
 
+@pytest.mark.parametrize("name,count", [("tiny_a", 24), ("tiny_d", 12)])
+def test_many_requests_decode_together(name, count, model_root):
+    """24 (12) requests at once in bfloat16: their decode steps are replayed graphs whose
+    products are the kernels for 17 to 32 (9 to 16) tokens, with the norms in their epilogues."""
+    spec, folder, config, weights, _ = _setup(name, model_root)
+    prompts = [tiny_configs.prompt_tokens(name, 3 + (7 * i) % 40, 50 + i) for i in range(count)]
+    engine = _engine(folder, spec, torch.bfloat16, capacity_tokens=4096, seqs=count)
+    got = engine.generate(prompts, 10)
+    assert [len(g) for g in got] == [10] * count
+    for prompt, g in zip(prompts, got):
+        _check_against_plain(config, weights, prompt, g, 0.0, 0, torch.bfloat16)
+    engine.cache.check_invariants()
+    assert engine.cache.num_free_pages() == engine.cache.num_pages and not engine.has_pending()
+
+
 def test_temperature_generation_is_seeded_and_matches_plain(model_root):
     spec, folder, config, weights, prompts = _setup("tiny_b", model_root)
     engine = _engine(folder, spec, torch.float32)
