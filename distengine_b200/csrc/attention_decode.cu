@@ -137,12 +137,13 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int qkv_stride,
 
     const size_t slab = (size_t)page * D;
     // keys and values of a tile from the cache; the token's own row is left out (fill_new)
-    // (a thread takes half a key's row: one look into the block table for its pieces)
+    // (two threads take a key's row, one look into the block table each; they alternate over
+    // the row's 16-byte pieces, so that every request of the pair fills a whole 32-byte sector)
     static_assert(THREADS == 2 * KT && CHUNKS % 2 == 0, "two threads a key row");
     auto load_tile = [&](int kt, int stage) {
         __nv_bfloat16* kd = k_s + stage * KT * LDS;
         __nv_bfloat16* vd = v_s + stage * KT * LDS;
-        const int j = threadIdx.x >> 1, ch0 = (threadIdx.x & 1) * (CHUNKS / 2);
+        const int j = threadIdx.x >> 1, ch0 = threadIdx.x & 1;
         const int kpos = kt + j;
         if (new_key && kpos == pos) return;
         bool ok = kpos >= lo && kpos < hi;
@@ -153,7 +154,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int qkv_stride,
             if (ok) off = ((size_t)page_id * kv_heads + hk) * slab + (size_t)(kpos % page) * D;
         }
 #pragma unroll
-        for (int ch = ch0; ch < ch0 + CHUNKS / 2; ++ch) {
+        for (int ch = ch0; ch < CHUNKS; ch += 2) {
             cp_async16(kd + j * LDS + ch * 8, k_pages + off + (ok ? ch * 8 : 0), ok);
             cp_async16(vd + j * LDS + ch * 8, v_pages + off + (ok ? ch * 8 : 0), ok);
         }
