@@ -556,9 +556,25 @@ DE_EXPORT int de_attn_decode_stamps(unsigned long long* host_out) {
 #endif
 DE_EXPORT int de_attn_decode_head_dim() { return D; }
 DE_EXPORT int de_attn_decode_max_cluster() { return MAX_CLUSTER; }
+// Blocks of the kernel that an SM holds at once (registers and shared memory), or 0 if unknown.
+DE_EXPORT int de_attn_decode_blocks_per_sm() {
+    static int blocks = -1;
+    if (blocks < 0) {
+        if (SMEM_BYTES > 48 * 1024 &&
+            cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 SMEM_BYTES) != cudaSuccess)
+            return 0;
+        int n = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attn_decode_kernel, THREADS,
+                                                          SMEM_BYTES) != cudaSuccess)
+            return 0;
+        blocks = n;
+    }
+    return blocks;
+}
 
-// `items`: tiles x `cap` work items (see the head of the file), `cluster` blocks a cluster (1, 2, 4
-// or 8; `cap` a multiple of it).  `partial_acc` / `partial_ml`: room for tiles * cap / cluster
+// `items`: tiles x `cap` work items (see the head of the file), `cluster` blocks a cluster (1 to 8;
+// `cap` a multiple of it).  `partial_acc` / `partial_ml`: room for tiles * cap / cluster
 // partial results (each kv_heads x 16 rows), used when cap > cluster.  `counters`: int32, one per
 // (tile, kv head), zero before the first launch.  `inv_freq` null: no rotation.  `write_kv` 0: the
 // layer reads a cache that an earlier layer of the step wrote, the token's key included.
@@ -573,8 +589,8 @@ DE_EXPORT int de_attn_decode(const void* qkv, int qkv_stride, void* out, int out
     if (num_items <= 0) return 0;
     if (head_dim != D || heads % kv_heads != 0) return -2;
     if (rot < 0 || rot > D || (rot & 1)) return -2;
-    if (cluster < 1 || cluster > MAX_CLUSTER || (cluster & (cluster - 1)) || cap < cluster ||
-        cap % cluster != 0 || num_items % cap != 0)
+    if (cluster < 1 || cluster > MAX_CLUSTER || cap < cluster || cap % cluster != 0 ||
+        num_items % cap != 0)
         return -4;
     if (cap > cluster && (partial_acc == nullptr || partial_ml == nullptr)) return -4;
     // 16-byte rows of keys and values

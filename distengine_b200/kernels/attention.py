@@ -79,6 +79,7 @@ class AttentionLauncher:
         # DISTENGINE_B200_DECODE_ATTENTION=split keeps them apart
         self.fused_decode = (self.tensor_cores and os.environ.get(
             "DISTENGINE_B200_DECODE_ATTENTION", "fused") != "split")
+        self._decode_blocks_per_sm: "int | None" = None     # asked of the kernel at first use
         self.key = (f"attention/{'mma' if self.tensor_cores else 'simt'}/{self.group}/"
                     f"{kv_heads}/{head_dim}/{self.window}")
 
@@ -118,8 +119,12 @@ class AttentionLauncher:
             span = int(host.seq_pos0.max()) + 1
         if self.window:
             span = min(span, self.window)
+        if self._decode_blocks_per_sm is None:
+            lib = library.load(*self.decode_module)
+            self._decode_blocks_per_sm = min(int(lib.de_attn_decode_blocks_per_sm()) or 4, 4)
         cluster, clusters, chunk = force_split or choose_decode_split(
-            tiles, self.kv_heads, span, int(os.environ.get("DISTENGINE_B200_DECODE_CLUSTER", "8")))
+            tiles, self.kv_heads, span, int(os.environ.get("DISTENGINE_B200_DECODE_CLUSTER", "8")),
+            self._decode_blocks_per_sm)
         if force_split is None:
             # the number of items is fixed by the cap (a replayed graph needs that); the chunk
             # length follows the step's longest range, so that the items share it evenly

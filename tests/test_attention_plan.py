@@ -65,14 +65,26 @@ def test_capped_plan_refuses_a_range_that_needs_more_chunks():
 @pytest.mark.parametrize("tiles,kv_heads,span", [(8, 4, 1024), (1, 4, 1024), (64, 4, 1024), (8, 4, 64),
                                                  (1, 4, 32768), (8, 4, 32768), (256, 8, 2048),
                                                  (1, 1, 1), (3, 5, 100000)])
-def test_decode_split_covers_the_span_with_whole_tiles_of_keys(tiles, kv_heads, span):
-    cluster, clusters, chunk = choose_decode_split(tiles, kv_heads, span)
-    assert cluster in (1, 2, 4, 8) and clusters >= 1
+@pytest.mark.parametrize("per_sm", [4, 3, 2])
+def test_decode_split_covers_the_span_with_whole_tiles_of_keys(tiles, kv_heads, span, per_sm):
+    cluster, clusters, chunk = choose_decode_split(tiles, kv_heads, span, per_sm=per_sm)
+    assert 1 <= cluster <= 8 and clusters >= 1
+    # one round of blocks over the SMs, unless even single blocks do not fit in one
+    assert cluster == 1 or tiles * kv_heads * cluster <= per_sm * 148
     assert chunk % 64 == 0 and chunk >= 64
     assert cluster * clusters * chunk >= span                # every key has an item
     assert chunk <= 2048 + 63                                # no block walks more than that
     if cluster > 1:
         assert span >= 64 * cluster // 2                     # no cluster of blocks without keys
+
+
+def test_decode_split_takes_sizes_between_the_powers_of_two():
+    # 64 tiles of one kv head each... 8 kv heads, three blocks an SM: 6 blocks a cluster fit, 8 not
+    assert choose_decode_split(8, 8, 4096, per_sm=3)[0] == 6
+    assert choose_decode_split(8, 8, 4096, per_sm=4)[0] == 8
+    assert choose_decode_split(8, 4, 520, per_sm=4)[0] == 8
+    assert choose_decode_split(64, 4, 520, per_sm=4)[0] == 2
+    assert choose_decode_split(20, 4, 520, per_sm=4)[0] == 4       # short ranges: powers of two
 
 
 def test_chunk_choice_fills_the_gpu_or_leaves_ranges_whole():

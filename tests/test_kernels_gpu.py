@@ -369,7 +369,8 @@ def test_decode_attention_in_one_launch(heads, kv_heads, d, page, rot, window, w
     # merge through global memory (twice on the same buffers: the counters must be zero again);
     # clusters of one block
     for split, repeats in ((None, 1), ((1, 1, 2048), 1), ((4, 1, 320), 1), ((8, 1, 192), 2),
-                           ((2, 3, 192), 3), ((1, 5, 256), 2), ((4, 2, 192), 1)):
+                           ((2, 3, 192), 3), ((1, 5, 256), 2), ((4, 2, 192), 1),
+                           ((6, 1, 256), 1), ((3, 2, 192), 2), ((7, 1, 192), 1), ((5, 1, 256), 1)):
         got, k_after, v_after = run_decode_attention(
             fx, qkv, heads, kv_heads, d, d ** -0.5, window, inv_freq, rot, writes, split=split,
             repeats=repeats)
