@@ -158,8 +158,6 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=MODEL["num_hidden_layers"],
                         help="fewer layers than the configuration's 22, for small profiling runs")
     parser.add_argument("--no-graphs", action="store_true")
-    parser.add_argument("--fused", action="store_true",
-                        help="decode steps of up to 16 tokens as one persistent kernel")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -186,8 +184,7 @@ def main() -> int:
     pages = (64 * (PROMPT + 3 + 2 * NEW_TOKENS + steps) + PREFILL) // PAGE + 64
     engine = Engine(folder, EngineConfig(dtype="bfloat16", block_size=PAGE, num_blocks=pages,
                                          decode_batch_size=64, max_batch_tokens=PREFILL,
-                                         use_graphs=not args.no_graphs,
-                                         use_fused=args.fused))
+                                         use_graphs=not args.no_graphs))
     runner, model = engine.runner, engine.model
     w_bytes, layer_params = weight_bytes(model)
     kv_per_token = sum(2 * g.k.shape[0] * g.spec.kv_heads * g.spec.head_dim * g.k.element_size()
@@ -301,7 +298,6 @@ def main() -> int:
                    "global_batch": args.batch, "seq_len": PROMPT, "new_tokens": steps,
                    "max_position": cfg.max_position_embeddings, "page_size": PAGE,
                    "parallelism": "single GPU", "cuda_graphs": bool(runner.graph_replays),
-                   "fused_decode_kernel": bool(runner.fused_steps),
                    "l2": "inputs larger than L2: 2.07 GB of weights are read every step",
                    "peaks": peak_kind},
         "clocks": clocks,

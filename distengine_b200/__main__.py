@@ -3,8 +3,10 @@
 ``generate`` follows the reference's ``utils.manual_generate`` (src/utils/manual_generate.py:10-58):
 ``--prompt`` and ``--max-new-tokens`` (default 32, must be positive) keep their names and
 meanings, and it prints the generated token ids and, with a tokenizer, the decoded text.  The
-reference downloads its model and tokenizer; here ``--model`` names a folder, ``--prompt-ids``
-gives token ids directly, and ``--prompt`` needs a ``tokenizer.json`` in the model folder.
+reference downloads its model and tokenizer; here ``--model`` names a folder (or ``--random``
+names a config.json, for which a random-weights model folder is written into a temporary folder
+from ``--weights-seed``), ``--prompt-ids`` gives token ids directly, and ``--prompt`` needs a
+``tokenizer.json`` in the model folder.
 ``--decode-batch-size`` is the reference's benchmark flag (src/utils/benchmark.py:593).
 ``random-model`` writes a model folder from a configuration and a seed.
 """
@@ -31,6 +33,25 @@ def _tokenizer(model_dir: str):
 def _generate(args: argparse.Namespace) -> int:
     if args.max_new_tokens <= 0:
         raise SystemExit("--max-new-tokens must be positive")
+    if (args.model is None) == (args.random is None):
+        raise SystemExit("give either --model DIR or --random CONFIG.json")
+    scratch = None
+    if args.random is not None:
+        import tempfile
+        from .weights.random_init import write_random_model
+        with open(args.random) as handle:
+            config_json = json.load(handle)
+        scratch = tempfile.TemporaryDirectory(prefix="distengine_b200-random-")
+        args.model = write_random_model(config_json, os.path.join(scratch.name, "model"),
+                                        args.weights_seed, dtype=args.dtype)
+    try:
+        return _generate_from_folder(args)
+    finally:
+        if scratch is not None:
+            scratch.cleanup()
+
+
+def _generate_from_folder(args: argparse.Namespace) -> int:
     from .config.engine import EngineConfig
     from .engine.engine import Engine
 
@@ -84,7 +105,10 @@ def main(argv: "list[str] | None" = None) -> int:
     sub = parser.add_subparsers(dest="command", required=True)
 
     gen = sub.add_parser("generate", help="generate tokens for one or more prompts")
-    gen.add_argument("--model", required=True, help="folder with config.json, model.safetensors")
+    gen.add_argument("--model", help="folder with config.json, model.safetensors")
+    gen.add_argument("--random", metavar="CONFIG", help="a config.json: generate with random "
+                     "weights of that shape instead of a model folder")
+    gen.add_argument("--weights-seed", type=int, default=0, help="seed of --random's weights")
     gen.add_argument("--prompt", action="append", help="prompt text (needs tokenizer.json)")
     gen.add_argument("--prompt-ids", action="append",
                      help="prompt as token ids, separated by spaces or commas; may repeat")

@@ -12,6 +12,11 @@ group of layers, and slots for per-request state of fixed size.
 * Pages are taken when a step is about to write positions (``reserve``, all requests of the step
   or none) and given back at ``release`` or when a window has passed them (``commit``).  The free
   list is last-in first-out, so pages are used again at once.
+* A step may be launched before its caller knows that it counts (the engine keeps the GPU one
+  decode step ahead of the host).  Such a step is committed *tentatively*: lengths advance, but no
+  page that a window has passed is given back and the state rows of its requests are copied aside
+  first.  ``confirm`` makes it final; ``rewind`` puts lengths and state rows back, and the pages
+  that the redone positions read are all still there.
 
 The reference's counterparts: ``BlockManager`` (src/distengine/block_manager.py:1-76: free list
 popped from the end, grow-only tables, everything returned at ``free``) and ``KVStorage``
@@ -115,12 +120,14 @@ class _StateGroup:
     spec: StateSpec
     entries: list[int]
     state: torch.Tensor                       # [layers, slots, *shape]
+    saved: "torch.Tensor | None" = None       # rows copied aside before a tentative step
 
 
 @dataclass
 class _Live:
     slot: int
     length: int = 0
+    confirmed: "int | None" = None            # length before the tentative steps, if any
 
 
 class CacheManager:
@@ -179,6 +186,11 @@ class CacheManager:
             sgroup.state = torch.zeros((len(sgroup.entries), max_seqs, *sgroup.spec.shape),
                                        dtype=sgroup.spec.dtype, device=self.device)
         self._reads = list(reads_cache_of)
+        # block-table rows travel through a pinned buffer of the manager's own: the host rows may
+        # change again (a release, the next reserve) while an earlier upload is still queued
+        self._stage: "torch.Tensor | None" = None
+        self._staged = torch.cuda.Event() if pin else None
+        self._stage_busy = False
 
     # ------------------------------------------------------------------ sizes
     @staticmethod
@@ -241,12 +253,14 @@ class CacheManager:
     def _missing(self, group: _PagedGroup, request_id: str, old_len: int,
                  new_len: int) -> list[int]:
         table = group.tables[request_id]
+        first = self._first_needed(group, old_len)
         if new_len <= len(table) * self.page_size and (old_len // self.page_size
                                                        == (new_len - 1) // self.page_size):
-            # the new positions lie in the page that holds the last position: it is held
-            if table and table[(new_len - 1) // self.page_size] >= 0:
+            # the new positions lie in the page that holds the last position: it is held, and so
+            # is everything before it unless a window's first page was given back
+            if (table and table[(new_len - 1) // self.page_size] >= 0
+                    and (group.spec.window is None or table[min(first, len(table) - 1)] >= 0)):
                 return []
-        first = self._first_needed(group, old_len)
         last = (new_len + self.page_size - 1) // self.page_size
         return [p for p in range(first, last) if p >= len(table) or table[p] < 0]
 
@@ -285,12 +299,35 @@ class CacheManager:
             group.host_table.numpy()[slot, missing] = pages
             self._mark(group, slot, missing[0], missing[-1] + 1)
 
-    def commit(self, request_id: str, new_len: int) -> None:
-        """The step wrote up to new_len; give back the pages a window has passed."""
+    def commit(self, request_id: str, new_len: int, tentative: bool = False) -> None:
+        """The step wrote up to new_len; give back the pages a window has passed.  ``tentative``:
+        the step may still be taken back (``rewind``), so nothing is given back until
+        ``confirm``; ``save_states`` must have copied the request's state rows aside before the
+        step was launched."""
         live = self._get(request_id)
         if new_len < live.length:
             raise ValueError("a request's length never shrinks")
+        if tentative:
+            if live.confirmed is None:
+                live.confirmed = live.length
+            live.length = new_len
+            return
+        if live.confirmed is not None:
+            raise ValueError(f"request '{request_id}' has a tentative step: confirm or rewind it "
+                             f"before the next final commit")
         live.length = new_len
+        self._pass_window(request_id, live)
+
+    def confirm(self, request_id: str) -> None:
+        """The tentative steps of the request count: what ``commit`` held back happens now."""
+        live = self._get(request_id)
+        if live.confirmed is None:
+            return
+        live.confirmed = None
+        self._pass_window(request_id, live)
+
+    def _pass_window(self, request_id: str, live: _Live) -> None:
+        new_len = live.length
         for group in self.paged:
             if group.spec.window is None:
                 continue
@@ -305,13 +342,29 @@ class CacheManager:
                     row[p] = -1
                 self._mark(group, live.slot, gone[0], gone[-1] + 1)
 
-    def rewind(self, request_id: str, length: int) -> None:
-        """Forget the tokens beyond ``length`` (a step that was launched ahead and is not used).
-        Pages stay with the request: it is about to need them again."""
+    def save_states(self, request_ids: "list[str]") -> None:
+        """Copy the state rows of these requests aside (on the current stream), before a
+        tentative step changes them.  Nothing to do for an architecture without such state."""
+        if not self.states:
+            return
+        index = torch.tensor([self._get(r).slot for r in request_ids], dtype=torch.long,
+                             device=self.device)
+        for sgroup in self.states:
+            if sgroup.saved is None:
+                sgroup.saved = torch.empty_like(sgroup.state)
+            sgroup.saved.index_copy_(1, index, sgroup.state.index_select(1, index))
+
+    def rewind(self, request_id: str) -> None:
+        """Take the request's tentative steps back: its length is what it was before them, its
+        state rows are the ones ``save_states`` copied (restored on the current stream, after the
+        kernels of the step that is taken back).  Pages stay with the request: it is about to
+        need them again, and a tentative commit has given none back."""
         live = self._get(request_id)
-        if length > live.length or length < 0:
-            raise ValueError("rewind goes back, and not below zero")
-        live.length = length
+        if live.confirmed is None:
+            raise ValueError(f"request '{request_id}' has no tentative step to take back")
+        live.length, live.confirmed = live.confirmed, None
+        for sgroup in self.states:
+            sgroup.state[:, live.slot].copy_(sgroup.saved[:, live.slot])
 
     def release(self, request_id: str) -> None:
         """Give back everything the request holds: its pages in every group and its slot."""
@@ -343,12 +396,32 @@ class CacheManager:
 
     # ------------------------------------------------------------------ device side
     def flush_tables(self) -> None:
-        """Bring the changed parts of the block tables to the device (on the current stream)."""
+        """Bring the changed parts of the block tables to the device (on the current stream).
+        The rows are first copied into a pinned buffer that nothing else writes until the upload
+        has happened, so the host may change its tables again at once."""
+        spans = [(group, slot, lo, hi) for group in self.paged
+                 for slot, (lo, hi) in group.dirty.items() if hi > lo]
         for group in self.paged:
-            for slot, (lo, hi) in group.dirty.items():
-                group.device_table[slot, lo:hi].copy_(group.host_table[slot, lo:hi],
-                                                      non_blocking=True)
             group.dirty.clear()
+        if not spans:
+            return
+        total = sum(hi - lo for _, _, lo, hi in spans)
+        if self._staged is None:                      # no CUDA device (tests of the host side)
+            for group, slot, lo, hi in spans:
+                group.device_table[slot, lo:hi].copy_(group.host_table[slot, lo:hi])
+            return
+        if self._stage_busy:
+            self._staged.synchronize()                # the earlier upload has left the buffer
+        if self._stage is None or self._stage.numel() < total:
+            self._stage = torch.empty(max(2 * total, 1024), dtype=torch.int32).pin_memory()
+        at = 0
+        for group, slot, lo, hi in spans:
+            piece = self._stage[at: at + hi - lo]
+            piece.copy_(group.host_table[slot, lo:hi])
+            group.device_table[slot, lo:hi].copy_(piece, non_blocking=True)
+            at += hi - lo
+        self._staged.record()
+        self._stage_busy = True
 
     def bindings(self) -> "list[CacheBinding | None]":
         """For every plan entry the cache its run is given."""

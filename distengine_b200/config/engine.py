@@ -38,8 +38,6 @@ class EngineConfig:
     max_batch_tokens: int = 2048         # token budget of one step
     max_model_len: int | None = None     # longest request; None: the model's max positions
     use_graphs: bool = True              # replay decode steps as CUDA graphs
-    use_fused: bool = False              # small decode steps as one persistent kernel (slower
-                                         # than the graph of kernels so far: off)
     device: str = "cuda:0"
 
     def __post_init__(self) -> None:

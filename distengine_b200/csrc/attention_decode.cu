@@ -19,8 +19,13 @@
 //     merges them in the arithmetic of `de_attn_combine`.  No block spins on another: the cluster
 //     barrier is the hardware's, and every block of a cluster reaches both barriers on every path.
 //   * the cache rows of earlier tokens are requested before the kernel waits for the kernel before
-//     it (programmatic dependent launch): that kernel is the product that made qkv and does not
-//     touch the cache, and everything before it is complete when this one starts.
+//     it (programmatic dependent launch).  They were written by earlier steps: between their
+//     writer and this launch lies at least one kernel that waited for its predecessor before it
+//     let its successor start (this kernel itself does, in the layer before), so the writer has
+//     completed.  That does not hold for a run that reads another run's cache (write_kv == 0):
+//     the key of this step's own token was stored there by a kernel of this same step, possibly
+//     with only early-triggering products in between, and is sure to be visible only after the
+//     wait; such a run requests its tiles after the wait.
 //
 // Items (attention_plan): every tile has `cap` consecutive items (its chunks in ascending order,
 // padded with empty ones), `cap` a multiple of the cluster size; block (g, hk, rank) of the grid
@@ -152,6 +157,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int qkv_stride,
             const int page_id = block_table[(size_t)slot * table_stride + kpos / page];
             ok = page_id >= 0 && page_id < num_pages;
             if (ok) off = ((size_t)page_id * kv_heads + hk) * slab + (size_t)(kpos % page) * D;
+            else if (ch0 == 0) atomicExch(status, 2);                // a visible key has no page
         }
 #pragma unroll
         for (int ch = ch0; ch < CHUNKS; ch += 2) {
@@ -168,11 +174,15 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int qkv_stride,
         *reinterpret_cast<uint4*>(dst + ch * 8) = *reinterpret_cast<const uint4*>(src + ch * 8);
     };
 
-    // the first tiles are requested before the wait (see the head of the file)
+    // the first tiles are requested before the wait, unless this step's own key is among what
+    // the cache is read for (see the head of the file)
+    const bool early = write_kv != 0;
+    if (early) {
 #pragma unroll
-    for (int t = 0; t < STAGES; ++t) {
-        if (k_lo + t * KT < hi) load_tile(k_lo + t * KT, t);
-        cp_async_commit();
+        for (int t = 0; t < STAGES; ++t) {
+            if (k_lo + t * KT < hi) load_tile(k_lo + t * KT, t);
+            cp_async_commit();
+        }
     }
 
     // what does not depend on qkv: the angles' cosines and sines, the page the token's key goes to
@@ -193,6 +203,13 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int qkv_stride,
 
     STAMP(1);
     pdl_wait();                                       // qkv is the previous kernel's output
+    if (!early) {
+#pragma unroll
+        for (int t = 0; t < STAGES; ++t) {
+            if (k_lo + t * KT < hi) load_tile(k_lo + t * KT, t);
+            cp_async_commit();
+        }
+    }
     __syncthreads();                                  // the cosines and sines are in place
     STAMP(2);
 

@@ -38,7 +38,7 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16
                 const int* __restrict__ seq_qstart, const int* __restrict__ seq_qlen,
                 const int* __restrict__ seq_pos0, const WorkItem* __restrict__ items,
                 float* __restrict__ partial_acc, float* __restrict__ partial_ml, int heads,
-                int kv_heads, int page, float scale, int window) {
+                int kv_heads, int page, float scale, int window, int* __restrict__ status) {
     static_assert(WN == 1 || RT == 1, "warps that split the keys own one row tile");
     constexpr int ROWS = WM * 16 * RT;     // rows of the tile
     constexpr int NK = KT / WN;            // keys of a tile that one warp sees
@@ -133,6 +133,7 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16
                 ok = page_id >= 0 && page_id < num_pages;
                 if (ok) off = ((size_t)page_id * kv_heads + hk) * slab + (size_t)(kpos % page) * D +
                               ch * 8;
+                else if (status != nullptr) atomicExch(status, 2);   // a visible key has no page
             }
             cp_async16(kd + j * LDS + ch * 8, k_pages + off, ok);
             cp_async16(vd + j * LDS + ch * 8, v_pages + off, ok);
@@ -355,7 +356,7 @@ int launch(const void* q, int q_stride, void* out, int out_stride, const void* k
            const void* v_pages, const int* block_table, int table_stride, int num_pages,
            const int* seq_slot, const int* seq_qstart, const int* seq_qlen, const int* seq_pos0,
            const int* items, int num_items, float* partial_acc, float* partial_ml, int heads,
-           int kv_heads, int page, float scale, int window, cudaStream_t s) {
+           int kv_heads, int page, float scale, int window, int* status, cudaStream_t s) {
     size_t smem = (size_t)4 * KT * LDS * sizeof(__nv_bfloat16);
     const size_t red = (size_t)WN * 16 * (D + 2) * sizeof(float);
     if (WN > 1 && red > smem) smem = red;
@@ -370,7 +371,7 @@ int launch(const void* q, int q_stride, void* out, int out_stride, const void* k
                      (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pages,
                      (const __nv_bfloat16*)v_pages, block_table, table_stride, num_pages, seq_slot,
                      seq_qstart, seq_qlen, seq_pos0, (const WorkItem*)items, partial_acc,
-                     partial_ml, heads, kv_heads, page, scale, window);
+                     partial_ml, heads, kv_heads, page, scale, window, status);
 }
 
 }  // namespace
@@ -387,7 +388,7 @@ DE_EXPORT int de_attn_mma(int shape, const void* q, int q_stride, void* out, int
                           const int* seq_qstart, const int* seq_qlen, const int* seq_pos0,
                           const int* items, int num_items, float* partial_acc, float* partial_ml,
                           int heads, int kv_heads, int head_dim, int page, float scale, int window,
-                          void* stream) {
+                          int* status, void* stream) {
     if (num_items <= 0) return 0;
     if (head_dim != D || heads % kv_heads != 0) return -2;
     if (q_stride % 2 != 0 || out_stride % 2 != 0) return -3;
@@ -396,9 +397,9 @@ DE_EXPORT int de_attn_mma(int shape, const void* q, int q_stride, void* out, int
         return launch<4, 1, WIDE_RT>(q, q_stride, out, out_stride, k_pages, v_pages, block_table,
                             table_stride, num_pages, seq_slot, seq_qstart, seq_qlen, seq_pos0, items,
                             num_items, partial_acc, partial_ml, heads, kv_heads, page, scale, window,
-                            s);
+                            status, s);
     return launch<1, 4, 1>(q, q_stride, out, out_stride, k_pages, v_pages, block_table, table_stride,
                         num_pages, seq_slot, seq_qstart, seq_qlen, seq_pos0, items, num_items,
-                        partial_acc, partial_ml, heads, kv_heads, page, scale, window, s);
+                        partial_acc, partial_ml, heads, kv_heads, page, scale, window, status, s);
 }
 

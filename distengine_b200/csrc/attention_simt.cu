@@ -12,6 +12,8 @@
 // keys.  Keys come straight from the pages through the block table
 // (position -> page, offset: src/distengine/paged_kv_cache.py:165-167); nothing is gathered or
 // expanded in memory (the reference copies and expands, paged_kv_cache.py:197-214,318-321).
+// A key inside a row's visible range whose page the block table does not hold is masked like a
+// key outside the range (never scored as zeros) and recorded in the status word (code 2).
 //
 // Long key ranges of decoded tokens are cut into chunks that separate blocks work on; each writes
 // an unnormalised partial result (accumulator, maximum, sum) into scratch memory, and
@@ -47,15 +49,16 @@ attn_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int
                  const int* __restrict__ seq_slot, const int* __restrict__ seq_qstart,
                  const int* __restrict__ seq_qlen, const int* __restrict__ seq_pos0,
                  const WorkItem* __restrict__ items, float* __restrict__ partial_acc,
-                 float* __restrict__ partial_ml, int heads, int kv_heads, int d, int page,
-                 float scale, int window) {
+                 float* __restrict__ partial_ml, int partial_limit, int heads, int kv_heads, int d,
+                 int page, float scale, int window, int* __restrict__ status) {
     extern __shared__ float smem[];
-    float* Ks = smem;                       // [TILE][d + 1]
+    float* Ks = smem;                       // [TILE][d + 1]; column d: 0, or -inf without a page
     float* Vs = Ks + TILE * (d + 1);        // [TILE][d]
     float* Qs = Vs + TILE * d;              // [ROWS][d]
 
     const WorkItem it = items[blockIdx.x];
-    if (it.kv_begin >= it.kv_end) {         // padding item
+    // (an item whose partial slot lies beyond the scratch it was given is skipped like padding)
+    if (it.kv_begin >= it.kv_end || it.partial >= partial_limit) {
         pdl_wait();
         return;
     }
@@ -100,9 +103,11 @@ attn_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int
             const int j = idx / d, dd = idx - j * d;
             const int kpos = kt + j;
             float kv = 0.0f, vv = 0.0f;
+            bool held = true;
             if (kpos >= k_lo_true && kpos < k_hi) {
                 const int page_id = block_table[(size_t)slot * table_stride + kpos / page];
-                if (page_id >= 0 && page_id < num_pages) {
+                held = page_id >= 0 && page_id < num_pages;
+                if (held) {
                     const size_t off =
                         ((size_t)page_id * kv_heads + hk) * slab + (size_t)(kpos % page) * d + dd;
                     kv = to_float(k_pages[off]);
@@ -111,13 +116,17 @@ attn_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int
             }
             Ks[j * (d + 1) + dd] = kv;
             Vs[j * d + dd] = vv;
+            if (dd == 0) {
+                Ks[j * (d + 1) + d] = held ? 0.0f : -INFINITY;
+                if (!held && status != nullptr) atomicExch(status, 2);
+            }
         }
         __syncthreads();
         if (!active) continue;
 
         const int kpos = kt + lane;
-        const bool valid = kpos >= row_lo && kpos < row_hi;
         const float* kr = Ks + lane * (d + 1);
+        const bool valid = kpos >= row_lo && kpos < row_hi && kr[d] == 0.0f;
         const float* qr = Qs + warp * d;
         float s = 0.0f;
         for (int dd = 0; dd < d; ++dd) s = fmaf(qr[dd], kr[dd], s);
@@ -173,11 +182,13 @@ __global__ void __launch_bounds__(ROWS * 32)
 attn_combine_kernel(T* __restrict__ out, int out_stride, const int* __restrict__ seq_qstart,
                     const int* __restrict__ seq_qlen, const CombineItem* __restrict__ items,
                     const float* __restrict__ partial_acc, const float* __restrict__ partial_ml,
-                    int heads, int kv_heads, int d, int rows_per_tile) {
+                    int partial_limit, int heads, int kv_heads, int d, int rows_per_tile) {
     const CombineItem it = items[blockIdx.x];
     pdl_wait();
     pdl_trigger();
     if (it.num_partials <= 0) return;
+    // slots beyond the scratch that was given: nothing is read, the rows are left as they are
+    if (it.first_partial < 0 || it.first_partial > partial_limit - it.num_partials) return;
     const int hk = blockIdx.y;
     const int g = heads / kv_heads;
     const int rows_total = seq_qlen[it.seq] * g;
@@ -222,13 +233,40 @@ attn_combine_kernel(T* __restrict__ out, int out_stride, const int* __restrict__
 
 DE_EXPORT int de_attn_simt_rows_per_tile() { return ROWS; }
 
+static int launch_simt(int dtype, const void* q, int q_stride, void* out, int out_stride,
+                       const void* k_pages, const void* v_pages, const int* block_table,
+                       int table_stride, int num_pages, const int* seq_slot,
+                       const int* seq_qstart, const int* seq_qlen, const int* seq_pos0,
+                       const int* items, int num_items, float* partial_acc, float* partial_ml,
+                       int partial_limit, int heads, int kv_heads, int d, int page, float scale,
+                       int window, int* status, void* stream);
+static int launch_combine(int dtype, void* out, int out_stride, const int* seq_qstart,
+                          const int* seq_qlen, const int* items, int num_items,
+                          const float* partial_acc, const float* partial_ml, int partial_limit,
+                          int heads, int kv_heads, int d, int rows_per_tile, void* stream);
+
 DE_EXPORT int de_attn_simt(int dtype, const void* q, int q_stride, void* out, int out_stride,
                            const void* k_pages, const void* v_pages, const int* block_table,
                            int table_stride, int num_pages, const int* seq_slot,
                            const int* seq_qstart, const int* seq_qlen, const int* seq_pos0,
                            const int* items, int num_items, float* partial_acc, float* partial_ml,
                            int heads, int kv_heads, int d, int page, float scale, int window,
-                           void* stream) {
+                           int* status, void* stream) {
+    return launch_simt(dtype, q, q_stride, out, out_stride, k_pages, v_pages, block_table,
+                       table_stride, num_pages, seq_slot, seq_qstart, seq_qlen, seq_pos0, items,
+                       num_items, partial_acc, partial_ml, 0x7fffffff, heads, kv_heads, d, page,
+                       scale, window, status, stream);
+}
+
+// `partial_limit`: partial slots that the scratch holds (work items that name a slot beyond it are
+// skipped); `status`: may be null.
+static int launch_simt(int dtype, const void* q, int q_stride, void* out, int out_stride,
+                       const void* k_pages, const void* v_pages, const int* block_table,
+                       int table_stride, int num_pages, const int* seq_slot,
+                       const int* seq_qstart, const int* seq_qlen, const int* seq_pos0,
+                       const int* items, int num_items, float* partial_acc, float* partial_ml,
+                       int partial_limit, int heads, int kv_heads, int d, int page, float scale,
+                       int window, int* status, void* stream) {
     if (num_items <= 0) return 0;
     if (d <= 0 || d > MAX_D || heads % kv_heads != 0) return -2;
     cudaStream_t s = (cudaStream_t)stream;
@@ -245,8 +283,8 @@ DE_EXPORT int de_attn_simt(int dtype, const void* q, int q_stride, void* out, in
         return de_launch(attn_simt_kernel<T>, grid, dim3(ROWS * 32), smem, s, (const T*)q,      \
                          q_stride, (T*)out, out_stride, (const T*)k_pages, (const T*)v_pages,   \
                          block_table, table_stride, num_pages, seq_slot, seq_qstart, seq_qlen,  \
-                         seq_pos0, (const WorkItem*)items, partial_acc, partial_ml, heads,      \
-                         kv_heads, d, page, scale, window);                                     \
+                         seq_pos0, (const WorkItem*)items, partial_acc, partial_ml,             \
+                         partial_limit, heads, kv_heads, d, page, scale, window, status);       \
     } while (0)
     if (dtype == DE_BF16) LAUNCH(__nv_bfloat16);
     LAUNCH(float);
@@ -259,6 +297,15 @@ DE_EXPORT int de_attn_combine(int dtype, void* out, int out_stride, const int* s
                               const int* seq_qlen, const int* items, int num_items,
                               const float* partial_acc, const float* partial_ml, int heads,
                               int kv_heads, int d, int rows_per_tile, void* stream) {
+    return launch_combine(dtype, out, out_stride, seq_qstart, seq_qlen, items, num_items,
+                          partial_acc, partial_ml, 0x7fffffff, heads, kv_heads, d, rows_per_tile,
+                          stream);
+}
+
+static int launch_combine(int dtype, void* out, int out_stride, const int* seq_qstart,
+                          const int* seq_qlen, const int* items, int num_items,
+                          const float* partial_acc, const float* partial_ml, int partial_limit,
+                          int heads, int kv_heads, int d, int rows_per_tile, void* stream) {
     if (num_items <= 0) return 0;
     if (d <= 0 || d > MAX_D) return -2;
     cudaStream_t s = (cudaStream_t)stream;
@@ -266,11 +313,11 @@ DE_EXPORT int de_attn_combine(int dtype, void* out, int out_stride, const int* s
     if (dtype == DE_BF16)
         return de_launch(attn_combine_kernel<__nv_bfloat16>, grid, dim3(ROWS * 32), 0, s,
                          (__nv_bfloat16*)out, out_stride, seq_qstart, seq_qlen,
-                         (const CombineItem*)items, partial_acc, partial_ml, heads, kv_heads, d,
-                         rows_per_tile);
+                         (const CombineItem*)items, partial_acc, partial_ml, partial_limit, heads,
+                         kv_heads, d, rows_per_tile);
     return de_launch(attn_combine_kernel<float>, grid, dim3(ROWS * 32), 0, s, (float*)out,
                      out_stride, seq_qstart, seq_qlen, (const CombineItem*)items, partial_acc,
-                     partial_ml, heads, kv_heads, d, rows_per_tile);
+                     partial_ml, partial_limit, heads, kv_heads, d, rows_per_tile);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -349,12 +396,14 @@ DE_EXPORT int de_attn_simt_static_scratch(
     }
     float* partial_acc = scratch;                               // [rows][head_dim]
     float* partial_ml = scratch + rows * head_dim;              // [rows][2]
-    int code = de_attn_simt(dtype, q, q_stride, out, out_stride, k_pages, v_pages, block_table,
-                            table_stride, num_pages, seq_slot, seq_qstart, seq_qlen, seq_pos0,
-                            items, num_items, partial_acc, partial_ml, heads, kv_heads, head_dim,
-                            page, scale, window, stream);
+    // the kernels are told how many partial slots the array holds for this call: an item that
+    // names a slot at or beyond num_partials writes and merges nothing
+    int code = launch_simt(dtype, q, q_stride, out, out_stride, k_pages, v_pages, block_table,
+                           table_stride, num_pages, seq_slot, seq_qstart, seq_qlen, seq_pos0,
+                           items, num_items, partial_acc, partial_ml, num_partials, heads,
+                           kv_heads, head_dim, page, scale, window, nullptr, stream);
     if (code != 0) return code;
-    return de_attn_combine(dtype, out, out_stride, seq_qstart, seq_qlen, combine_items,
-                           num_combine, partial_acc, partial_ml, heads, kv_heads, head_dim, ROWS,
-                           stream);
+    return launch_combine(dtype, out, out_stride, seq_qstart, seq_qlen, combine_items,
+                          num_combine, partial_acc, partial_ml, num_partials, heads, kv_heads,
+                          head_dim, ROWS, stream);
 }

@@ -22,6 +22,10 @@
 //   * num_partials * kv_heads * 8 * (head_dim + 2) must not exceed DE_ATTN_STATIC_SCRATCH_FLOATS.
 //     A larger request is refused: the function returns DE_ATTN_STATIC_TOO_LARGE, launches
 //     nothing, and de_attn_static_scratch_error() gives the sizes in words.
+//   * `num_partials` is the number of partial slots the work items use; it is what the size check
+//     is made with, so the kernels are told it too: a work item or combine item that names a
+//     slot at or beyond num_partials is skipped (it writes nothing into the array or beyond it,
+//     and the rows it would have produced are left as they were in `out`).
 //   * It calls no cudaMalloc, cudaFree or other allocating routine, on any call.
 //   * The first call on a device looks up the array's device address
 //     (cudaGetSymbolAddress, with that device current) and keeps it; make that first call

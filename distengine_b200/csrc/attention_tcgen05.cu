@@ -358,6 +358,7 @@ attn_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
                 if (p < pages_per_tile && first + page > k_lo_true && first < k_hi) {
                     id[i] = block_table[(size_t)slot * table_stride + first / page];
                     if (id[i] >= num_pages) id[i] = -1;
+                    if (id[i] < 0) atomicExch(status, 2);            // visible keys have no page
                 }
             }
         };

@@ -66,8 +66,12 @@ static inline int de_check(cudaError_t e) { return e == cudaSuccess ? 0 : (int)e
 // 10% slower than no overlap at all, because the waiting blocks took the place of blocks of the
 // running kernel that had not started yet; triggering late made them 3% faster).  The decode
 // products, whose blocks are all resident at once, trigger right after their first loads.  Every
-// kernel calls pdl_wait() on all paths, so completion is transitive along the stream.  Without
-// the launch attribute both calls do nothing.
+// kernel calls pdl_wait() on all paths, so completion is transitive along the stream: once a
+// kernel's wait has returned, every kernel before it has completed.  Before its wait a kernel
+// knows less: only that the kernels before the last one that triggered after its own wait have
+// completed (a chain of products that trigger at their start can all be resident at once).  So
+// what is read before the wait must not have been written later than that.  Without the launch
+// attribute both calls do nothing.
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void pdl_trigger() {
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");

@@ -52,11 +52,11 @@ class Engine:
         self.cache = CacheManager(specs, [e.reads_cache_of for e in self.model.plan],
                                   cfg.block_size, num_blocks, cfg.decode_batch_size, max_len,
                                   cfg.dtype, device)
+        self.sampler = Sampler(device, cfg.decode_batch_size)
         self.runner = StepRunner(self.model, self.cache, use_graphs=cfg.use_graphs,
-                                 use_fused=cfg.use_fused)
+                                 status=self.sampler.status)
         self.scheduler = Scheduler(self.cache, cfg.max_batch_tokens, cfg.decode_batch_size,
                                    max_len, self.model.config.vocabulary)
-        self.sampler = Sampler(device, cfg.decode_batch_size)
         self.completed: deque[dict] = deque()
         self._flying = None                     # (plan, sampler ticket) of the step that is running
         self.requests: dict[str, Request] = {}
@@ -96,12 +96,15 @@ class Engine:
         plan, ticket = flying
         ahead = self._start_ahead(plan)                       # before this step's tokens are known
         tokens = self.sampler.wait(ticket)
+        self.runner.check_status(self.sampler.last_status)     # came to the host with the ids
         self.steps += 1
         self.tokens_fed += plan.num_tokens
         finished = self.scheduler.update(plan, tokens)
         if self.scheduler.has_pending():
             following = self.scheduler.schedule()
             if ahead is not None and self._same_step(ahead[0], following):
+                for entry in ahead[0].entries:
+                    self.cache.confirm(entry.request_id)
                 self._flying = (following, ahead[1])
             else:
                 if ahead is not None:
@@ -160,17 +163,18 @@ class Engine:
                               [r.num_tokens + 1 for r in running])
         prepared = self.runner.prepare(entries, extra)
         # the ids this step feeds are the ones the running step is about to sample
-        logits = self.runner.launch(prepared, token_source=self.sampler.ids[: len(running)])
+        logits = self.runner.launch(prepared, token_source=self.sampler.ids[: len(running)],
+                                    tentative=True)
         return prepared, self.sampler.launch(logits, self.runner.last_arrays)
 
     def _take_back(self, prepared) -> None:
         """A step that was started ahead and is not the scheduler's plan: its requests that still
-        run go back to the length they had (what it wrote to the cache lies beyond it and is
-        written again).  The GPU work itself is lost."""
+        run go back to where they were: their lengths, and whatever fixed-size state the step
+        advanced (keys and values that it wrote lie beyond the length and are written again; no
+        page that a window had passed was given back meanwhile).  The GPU work itself is lost."""
         for entry in prepared.entries:
             if self.cache.has(entry.request_id):
-                self.cache.rewind(entry.request_id,
-                                  self.cache.length(entry.request_id) - len(entry.tokens))
+                self.cache.rewind(entry.request_id)
 
     def drain_completed(self) -> list[dict]:
         results = list(self.completed)

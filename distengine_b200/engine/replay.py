@@ -37,7 +37,7 @@ LIVE_REQUESTS = 8          # slots; a trace holds up to four live requests
 
 def build_runner(model_dir: str, dtype: "str | torch.dtype", max_tokens: int,
                  page_size: int = 16, device: str = "cuda:0",
-                 poison_freed_pages: bool = False, use_fused: bool = False) -> StepRunner:
+                 poison_freed_pages: bool = False, use_graphs: bool = False) -> StepRunner:
     """Model, cache for ``max_tokens`` tokens (in pages of ``page_size``) and the step runner."""
     dtype = parse_dtype(dtype)
     model = load_model(model_dir, dtype, device)
@@ -48,7 +48,7 @@ def build_runner(model_dir: str, dtype: "str | torch.dtype", max_tokens: int,
     cache = CacheManager(model.cache_specs(), [e.reads_cache_of for e in model.plan], page_size,
                          num_pages, LIVE_REQUESTS, max_len, dtype, model.device,
                          poison_freed_pages=poison_freed_pages)
-    return StepRunner(model, cache, use_fused=use_fused)
+    return StepRunner(model, cache, use_graphs=use_graphs)
 
 
 def replay(runner: StepRunner, lines: IO[str], out_dir: str, log: IO[str] = sys.stdout) -> None:

@@ -75,15 +75,10 @@ class Request:
     def is_finished(self) -> bool:
         return self.status == RequestStatus.FINISHED
 
-    def start(self) -> None:
-        if self.status != RequestStatus.WAITING:
-            raise RuntimeError("Can't start this request because the request status is not "
-                               "WAITING")
-        self.status = RequestStatus.RUNNING
-
     def append_token(self, token_id: int) -> None:
         if self.status != RequestStatus.RUNNING:
-            raise RuntimeError("This request is not in RUNNING state")
+            raise RuntimeError(f"request '{self.request_id}' is {self.status.name}: only a "
+                               f"running request takes a new token")
         self.generated_token_ids.append(token_id)
         if token_id == self.eos_token_id:
             self.reason = "eos"

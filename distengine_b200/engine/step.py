@@ -41,7 +41,6 @@ class PreparedStep:
     host: SimpleNamespace
     prep: StepPrep
     graph_shape: "dict | None"
-    fused: bool
     views: dict
     offsets: list
     total: int
@@ -57,13 +56,17 @@ def _align(n: int) -> int:
 
 class StepRunner:
     def __init__(self, model, cache: CacheManager, use_graphs: bool = False,
-                 use_fused: bool = False) -> None:
+                 status: "torch.Tensor | None" = None) -> None:
+        """``status``: the int32 [1] device word in which kernels record skipped work; the
+        runner makes its own unless the caller wants it somewhere (beside the sampled ids, so
+        that it comes to the host with them)."""
         self.model, self.cache = model, cache
         self.device, self.dtype = model.device, model.dtype
         ops.require_device(self.device)
         self.vocabulary = model.config.vocabulary
         self.workspace = Workspace(self.device)
-        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.status = (status if status is not None
+                       else torch.zeros(1, dtype=torch.int32, device=self.device))
         self._host_meta: "torch.Tensor | None" = None        # pinned int32 staging
         self._dev_meta: "torch.Tensor | None" = None
         self._uploaded = torch.cuda.Event()
@@ -77,12 +80,6 @@ class StepRunner:
         self._meta_generation = 0
         self._layouts: dict[tuple, tuple] = {}
         self.graph_replays = 0
-        # the whole decode step as one persistent kernel, where the model has the shape for it
-        self.fused = None
-        if use_fused and hasattr(model, "blocks"):
-            from ..models.fused_decode import FusedDecoder
-            self.fused = FusedDecoder.try_build(model, cache)
-        self.fused_steps = 0
 
     # ------------------------------------------------------------------ host side
     def _validate(self, entries: list[StepEntry]) -> None:
@@ -195,30 +192,32 @@ class StepRunner:
             raise
         host = self._host_arrays(entries)
         graph_shape = None
-        fused = self.fused is not None and self.fused.takes(host)
-        if (self.use_graphs and not fused and int(host.seq_qlen.max()) == 1
+        if (self.use_graphs and int(host.seq_qlen.max()) == 1
                 and getattr(self.model, "graph_safe", True)):
             # a pure decode step: shape its arrays by the batch's shape only, so that it can be
             # replayed; the key range is capped at the next multiple of 512 positions
             longest = int(host.seq_pos0.max()) + 1
             graph_shape = {"context_cap": (longest + 511) // 512 * 512}
         prep = StepPrep(host, graph_shape)
-        if not fused:
-            self.model.prepare(prep)
+        self.model.prepare(prep)
         for name, array in (extra or {}).items():
             prep.add(name, array)
         views, offsets, total, arrays = self._stage(host, prep)
-        return PreparedStep(entries, host, prep, graph_shape, fused, views, offsets, total)
+        return PreparedStep(entries, host, prep, graph_shape, views, offsets, total)
 
-    def launch(self, prepared: "PreparedStep",
-               token_source: "torch.Tensor | None" = None) -> torch.Tensor:
+    def launch(self, prepared: "PreparedStep", token_source: "torch.Tensor | None" = None,
+               tentative: bool = False) -> torch.Tensor:
         """The device half: upload the prepared arrays, run the model, advance the cache's
         lengths.  Returns logits float32 [wanted, vocabulary] on the device, in the order of the
         entries and of each entry's ``want``; the tensor is reused by the next step.
         ``token_source`` (int32 on the device, one id per token of the step): the token ids are
         taken from there instead of from the prepared arrays - ids that an earlier kernel in the
-        stream produces and the host has not seen yet."""
+        stream produces and the host has not seen yet.
+        ``tentative``: the caller may take the step back (``CacheManager.rewind``) or make it
+        final (``CacheManager.confirm``): the cache keeps everything that a redo would need."""
         host, prep, views = prepared.host, prepared.prep, prepared.views
+        if tentative:
+            self.cache.save_states([e.request_id for e in prepared.entries])
         total = prepared.total
         self._dev_meta[:total].copy_(self._host_meta[:total], non_blocking=True)
         if token_source is not None:
@@ -238,15 +237,13 @@ class StepRunner:
             arrays={k: v for k, v in views.items() if k not in self._BASE},
             notes=prep.notes, workspace=self.workspace, status=self.status)
         self.last_arrays = ctx.arrays
-        if prepared.fused:
-            logits = self.fused.run(ctx)
-            self.fused_steps += 1
-        elif prepared.graph_shape is None:
+        if prepared.graph_shape is None:
             logits = self.model.forward(ctx, self.bindings)
         else:
             logits = self._forward_graphed(ctx, prep, prepared.graph_shape)
         for e in prepared.entries:
-            self.cache.commit(e.request_id, self.cache.length(e.request_id) + len(e.tokens))
+            self.cache.commit(e.request_id, self.cache.length(e.request_id) + len(e.tokens),
+                              tentative=tentative)
         self.steps_run += 1
         return logits
 
@@ -308,12 +305,15 @@ class StepRunner:
     def release(self, request_id: str) -> None:
         self.cache.release(request_id)
 
-    def check_status(self) -> None:
-        """Synchronises; raises if a kernel skipped work since the last check."""
-        code = int(self.status.item())
+    def check_status(self, code: "int | None" = None) -> None:
+        """Raises if a kernel skipped work since the last check.  ``code``: the status word as
+        the caller has already read it; without it the word is read here (a synchronisation)."""
+        if code is None:
+            code = int(self.status.item())
         if code != 0:
             self.status.zero_()
             what = {1: "a token's position had no page in its request's block table",
+                    2: "a key that a token reads had no page in its request's block table",
                     3: "a bounded wait inside a tcgen05 kernel ran out",
                     4: "a tcgen05 kernel found its shared memory misaligned"}.get(
                         code, "unknown code")

@@ -51,7 +51,8 @@ class AttentionLauncher:
     """Plans and runs the attention of all layers that share one shape of heads."""
 
     def __init__(self, dtype: torch.dtype, heads: int, kv_heads: int, head_dim: int,
-                 scale: float, window: "int | None") -> None:
+                 scale: float, window: "int | None",
+                 device: "torch.device | None" = None) -> None:
         check_head_dim(head_dim)
         if heads % kv_heads != 0:
             raise ValueError(f"heads ({heads}) must be a multiple of kv_heads ({kv_heads})")
@@ -80,6 +81,8 @@ class AttentionLauncher:
         self.fused_decode = (self.tensor_cores and os.environ.get(
             "DISTENGINE_B200_DECODE_ATTENTION", "fused") != "split")
         self._decode_blocks_per_sm: "int | None" = None     # asked of the kernel at first use
+        self._device = device
+        self._sm_count: "int | None" = None                 # asked of the device at first use
         self.key = (f"attention/{'mma' if self.tensor_cores else 'simt'}/{self.group}/"
                     f"{kv_heads}/{head_dim}/{self.window}")
 
@@ -87,6 +90,13 @@ class AttentionLauncher:
         """Blocks an SM holds at once: one of the tcgen05 kernel (it takes nearly all shared
         memory), about two of the others; key ranges are only cut when there are fewer tiles."""
         return 1 if any(shape.code == 2 for shape in self.shapes) else 2
+
+    def sm_count(self) -> int:
+        """SMs of the device the layer runs on (the current one if none was named)."""
+        if self._sm_count is None:
+            device = self._device if self._device is not None else torch.cuda.current_device()
+            self._sm_count = int(torch.cuda.get_device_properties(device).multi_processor_count)
+        return self._sm_count
 
     def modules(self) -> list[tuple[str, tuple[str, ...]]]:
         """The kernel libraries this launcher calls (to compile them side by side up front)."""
@@ -124,7 +134,7 @@ class AttentionLauncher:
             self._decode_blocks_per_sm = min(int(lib.de_attn_decode_blocks_per_sm()) or 4, 4)
         cluster, clusters, chunk = force_split or choose_decode_split(
             tiles, self.kv_heads, span, int(os.environ.get("DISTENGINE_B200_DECODE_CLUSTER", "8")),
-            self._decode_blocks_per_sm)
+            self._decode_blocks_per_sm, sm_count=self.sm_count())
         if force_split is None:
             # the number of items is fixed by the cap (a replayed graph needs that); the chunk
             # length follows the step's longest range, so that the items share it evenly
@@ -185,7 +195,8 @@ class AttentionLauncher:
             elif prep.graph_shape is not None:
                 cap = int(prep.graph_shape["context_cap"])
                 span = cap if not self.window else min(cap, self.window + int(host.seq_qlen.max()))
-                chunk = choose_chunk(total_tiles, self.kv_heads, span, self._blocks_per_sm())
+                chunk = choose_chunk(total_tiles, self.kv_heads, span, self._blocks_per_sm(),
+                                     sm_count=self.sm_count())
                 if chunk:
                     chunks_cap = (span + chunk - 1) // chunk + (1 if self.window else 0)
             elif int(qlen.sum()):
@@ -193,7 +204,8 @@ class AttentionLauncher:
                 longest = int((host.seq_pos0[live] + qlen[live]).max())
                 if self.window:
                     longest = min(longest, self.window + int(qlen.max()))
-                chunk = choose_chunk(total_tiles, self.kv_heads, longest, self._blocks_per_sm())
+                chunk = choose_chunk(total_tiles, self.kv_heads, longest, self._blocks_per_sm(),
+                                     sm_count=self.sm_count())
             plan = build_plan(qlen, host.seq_pos0, self.group, self.kv_heads, shape.rows,
                               self.window, chunk, chunks_cap)
             prep.add(f"{self.key}/{shape.name}/items", plan.items)
@@ -301,19 +313,21 @@ def launch_items(code: int, module, q, out, k_pages, v_pages, block_table, seq_s
               k_pages.shape[0], seq_slot.data_ptr(), seq_qstart.data_ptr(), seq_qlen.data_ptr(),
               seq_pos0.data_ptr(), items.data_ptr(), items.shape[0], _ptr(partial_acc),
               _ptr(partial_ml), heads, kv_heads, head_dim, k_pages.shape[2], float(scale),
-              int(window or 0), _stream())
+              int(window or 0))
+    global _status_fallback
+    if status is None:
+        if _status_fallback is None or _status_fallback.device != q.device:
+            _status_fallback = torch.zeros(1, dtype=torch.int32, device=q.device)
+        status = _status_fallback
     if code < 0:
-        _check(lib.de_attn_simt(_tag(q.dtype), *common), "paged attention")
+        _check(lib.de_attn_simt(_tag(q.dtype), *common, status.data_ptr(), _stream()),
+               "paged attention")
     elif code == 2:
-        global _status_fallback
-        if status is None:
-            if _status_fallback is None or _status_fallback.device != q.device:
-                _status_fallback = torch.zeros(1, dtype=torch.int32, device=q.device)
-            status = _status_fallback
-        _check(lib.de_attn_tcgen05(*common[:-1], status.data_ptr(), common[-1]),
+        _check(lib.de_attn_tcgen05(*common, status.data_ptr(), _stream()),
                "paged attention (tcgen05)")
     else:
-        _check(lib.de_attn_mma(code, *common), "paged attention (tensor cores)")
+        _check(lib.de_attn_mma(code, *common, status.data_ptr(), _stream()),
+               "paged attention (tensor cores)")
     if combine is not None and combine.shape[0] > 0:
         _i32(combine, "combine")
         merge = library.load("attention_simt")

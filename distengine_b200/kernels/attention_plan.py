@@ -17,7 +17,6 @@ from dataclasses import dataclass
 
 import numpy as np
 
-SM_COUNT = 148
 CHUNKS = (2048, 1024, 512, 256, 128, 64)
 
 
@@ -59,10 +58,11 @@ def _longest_first(items: np.ndarray, lo: np.ndarray) -> np.ndarray:
     return items[np.argsort(-keys, kind="stable")]
 
 
-def choose_chunk(num_tiles: int, kv_heads: int, longest: int, blocks_per_sm: int = 2) -> int:
-    """The largest chunk that still gives every SM ``blocks_per_sm`` blocks (as many as the
-    kernel has resident at once); 0: do not split."""
-    wanted = blocks_per_sm * SM_COUNT
+def choose_chunk(num_tiles: int, kv_heads: int, longest: int, blocks_per_sm: int = 2, *,
+                 sm_count: int) -> int:
+    """The largest chunk that still gives every one of the device's ``sm_count`` SMs
+    ``blocks_per_sm`` blocks (as many as the kernel has resident at once); 0: do not split."""
+    wanted = blocks_per_sm * sm_count
     if num_tiles * kv_heads >= wanted:
         return 0
     for chunk in CHUNKS:
@@ -72,28 +72,29 @@ def choose_chunk(num_tiles: int, kv_heads: int, longest: int, blocks_per_sm: int
 
 
 def choose_decode_split(num_tiles: int, kv_heads: int, span: int, max_cluster: int = 8,
-                        per_sm: int = 4) -> tuple[int, int, int]:
+                        per_sm: int = 4, *, sm_count: int) -> tuple[int, int, int]:
     """How the one-launch decode kernel cuts key ranges of up to ``span`` keys:
     (blocks a cluster, clusters a tile, chunk length).  The chunks of a cluster merge through
     shared memory; several clusters a tile merge through global memory, which costs a few
     microseconds, so a tile gets more than one cluster only when ranges are long and the step
-    would otherwise leave most of the GPU idle.  ``per_sm``: blocks of the kernel an SM holds."""
+    would otherwise leave most of the GPU idle.  ``per_sm``: blocks of the kernel an SM holds;
+    ``sm_count``: SMs of the device."""
     blocks = max(num_tiles * kv_heads, 1)
     tiles_of_keys = max((span + 63) // 64, 1)
     cluster = 1
     # one round of blocks over the SMs at most, and no block without a whole tile of 64 keys
     per_sm = int(os.environ.get("DISTENGINE_B200_DECODE_BLOCKS_PER_SM", str(per_sm)))
-    while (cluster < max_cluster and blocks * cluster * 2 <= per_sm * SM_COUNT
+    while (cluster < max_cluster and blocks * cluster * 2 <= per_sm * sm_count
            and cluster * 2 <= tiles_of_keys):
         cluster *= 2
     # where the next power of two would not fit in one round, a size in between may; it pays for
     # long ranges only (measured: 4,096 keys at head size 128, 6 blocks a cluster against 8 in two
     # rounds, 61 against 76 us; 520 keys at batch 20, 7 against 4, 3 % slower a step)
-    while (cluster < max_cluster and blocks * (cluster + 1) <= per_sm * SM_COUNT
+    while (cluster < max_cluster and blocks * (cluster + 1) <= per_sm * sm_count
            and span >= (cluster + 1) * 512):
         cluster += 1
     clusters = (span + cluster * 2048 - 1) // (cluster * 2048)          # 2048 keys a block at most
-    while (blocks * cluster * clusters < 2 * SM_COUNT
+    while (blocks * cluster * clusters < 2 * sm_count
            and span >= cluster * (clusters + 1) * 256):                   # 256 keys a block at least
         clusters += 1
     per_block = (span + cluster * clusters - 1) // (cluster * clusters)
@@ -103,8 +104,9 @@ def choose_decode_split(num_tiles: int, kv_heads: int, span: int, max_cluster: i
 
 def build_plan(seq_qlen: np.ndarray, seq_pos0: np.ndarray, group: int, kv_heads: int,
                rows_per_tile: int, window: int = 0, chunk: "int | None" = None,
-               chunks_cap: "int | None" = None, sort: bool = True) -> AttentionPlan:
-    """``chunk`` None: chosen from the step's shape.  ``chunks_cap`` (with a given chunk): every
+               chunks_cap: "int | None" = None, sort: bool = True,
+               sm_count: "int | None" = None) -> AttentionPlan:
+    """``chunk`` None: chosen from the step's shape and the device's ``sm_count``.  ``chunks_cap`` (with a given chunk): every
     tile gets exactly that many items and one combine item, padded with empty ones, so that the
     arrays' shapes depend on the number of tiles only (what a replayed CUDA graph needs).
     ``sort`` false keeps the items in the order of the tiles and their chunks."""
@@ -112,7 +114,10 @@ def build_plan(seq_qlen: np.ndarray, seq_pos0: np.ndarray, group: int, kv_heads:
     total = len(seq)
     if chunk is None:
         longest = int((hi - lo).max()) if total else 0
-        chunk = choose_chunk(total, kv_heads, longest)
+        if sm_count is None:
+            raise ValueError("build_plan chooses the chunk itself only when it is told the "
+                             "device's number of SMs")
+        chunk = choose_chunk(total, kv_heads, longest, sm_count=sm_count)
     if chunk == 0 or total == 0:
         items = np.zeros((total, 8), dtype=np.int32)
         items[:, 0], items[:, 1], items[:, 2], items[:, 3], items[:, 4] = seq, row0, 0, hi, -1

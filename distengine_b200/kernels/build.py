@@ -38,7 +38,6 @@ MODULES: dict[str, tuple[str, tuple[str, ...]]] = {
     "attention_decode": ("attention_decode.cu", ()),    # built per head size: HEAD_DIM=<d>
     "linear_mid": ("linear_mid.cu", ("cuda",)),
     "attention_tcgen05": ("attention_tcgen05.cu", ()),  # built per head size: HEAD_DIM=64|128
-    "decode_fused": ("decode_fused.cu", ()),            # built per head size: HEAD_DIM=<d>
 }
 
 

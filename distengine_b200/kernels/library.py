@@ -34,7 +34,8 @@ SIGNATURES: dict[str, dict[str, list]] = {
     },
     "attention_simt": {
         "de_attn_simt_rows_per_tile": [],
-        "de_attn_simt": [I, P, I, P, I, P, P, P, I, I, P, P, P, P, P, I, P, P, I, I, I, I, F, I, P],
+        "de_attn_simt": [I, P, I, P, I, P, P, P, I, I, P, P, P, P, P, I, P, P, I, I, I, I, F, I, P,
+                         P],
         "de_attn_combine": [I, P, I, P, P, P, I, P, P, I, I, I, I, P],
     },
     "linear_small": {
@@ -51,18 +52,14 @@ SIGNATURES: dict[str, dict[str, list]] = {
         "de_gemm_tcgen05": [P, I, P, I, P, I, I, I, I, I, I, P, P],
         "de_gemm_tcgen05_tile": [I, I, I], "de_gemm_tcgen05_sms": [],
     },
-    "decode_fused": {
-        "de_decode_fused_head_dim": [], "de_decode_fused_max_tokens": [],
-        "de_decode_fused_args_bytes": [], "de_decode_fused_layer_bytes": [],
-        "de_decode_fused_grid": [I], "de_decode_fused": [P, I, P],
-    },
     "attention_tcgen05": {
         "de_attn_tcgen05_rows": [], "de_attn_tcgen05_head_dim": [],
         "de_attn_tcgen05": [P, I, P, I, P, P, P, I, I, P, P, P, P, P, I, P, P, I, I, I, I, F, I, P, P],
     },
     "attention_mma": {
         "de_attn_mma_head_dim": [], "de_attn_mma_rows": [I],
-        "de_attn_mma": [I, P, I, P, I, P, P, P, I, I, P, P, P, P, P, I, P, P, I, I, I, I, F, I, P],
+        "de_attn_mma": [I, P, I, P, I, P, P, P, I, I, P, P, P, P, P, I, P, P, I, I, I, I, F, I, P,
+                        P],
     },
     "attention_decode": {
         "de_attn_decode_head_dim": [], "de_attn_decode_max_cluster": [],
@@ -84,13 +81,11 @@ def default_build_requests() -> list[tuple[str, tuple[str, ...]]]:
     """Every module; the per-head-size attention for the head sizes of common models."""
     requests = [(module, ()) for module in _build.MODULES
                 if module in SIGNATURES
-                and module not in ("attention_mma", "attention_decode", "decode_fused",
-                                   "attention_tcgen05")]
+                and module not in ("attention_mma", "attention_decode", "attention_tcgen05")]
     # (16: the head size of the tiny model that the smoke test generates with)
     return (requests + [("attention_mma", (f"HEAD_DIM={d}",)) for d in (16, 64, 128)]
             + [("attention_tcgen05", (f"HEAD_DIM={d}",)) for d in (64, 128)]
-            + [("attention_decode", (f"HEAD_DIM={d}",)) for d in (16, 64, 128)]
-            + [("decode_fused", (f"HEAD_DIM={d}",)) for d in (64, 128)])
+            + [("attention_decode", (f"HEAD_DIM={d}",)) for d in (16, 64, 128)])
 
 
 def load(module: str, defines: tuple[str, ...] = ()) -> ctypes.CDLL:

@@ -31,7 +31,7 @@ class PagedAttention(Mixer):
         self.width, self.heads, self.kv_heads, self.head_dim = width, heads, kv_heads, head_dim
         self.scale, self.window = float(scale), window
         self.position = build_position_encoding(position, dtype, device)
-        self.kernels = AttentionLauncher(dtype, heads, kv_heads, head_dim, scale, window)
+        self.kernels = AttentionLauncher(dtype, heads, kv_heads, head_dim, scale, window, device)
         self.w_qkv: "torch.Tensor | None" = None
         self.w_o: "torch.Tensor | None" = None
 

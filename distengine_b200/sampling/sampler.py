@@ -5,7 +5,8 @@ Greedy is the reference's only sampler: arg-max over the vocabulary
 softmax(logits / T), computed in 32-bit, by the Gumbel-max rule with counter-based uniforms of
 (seed, position of the sampled token, token id): a request's draws depend on its own seed and
 position only, not on the batch it shares or on how its prompt was cut.  Temperature 0 is greedy.
-Both run in one kernel over the step's logits rows; the sampled ids come back in one small copy.
+Both run in one kernel over the step's logits rows; the sampled ids come back in one small copy,
+and with them the status word in which the step's kernels record work that they had to skip.
 """
 
 from __future__ import annotations
@@ -29,15 +30,24 @@ def pack_sampling(temperatures: list[float], seeds: list[int], positions: list[i
 
 class Sampler:
     """Two launches may be outstanding (the engine starts the next step before it has read this
-    step's ids): the ids travel to the host through two pinned buffers in turn."""
+    step's ids): the ids travel to the host through two pinned buffers in turn.
+
+    ``status`` (int32 [1]) lies directly before ``ids`` in one device buffer, so that one copy
+    brings both to the host: a step runner that is given it as its status word has its kernels'
+    complaints read at every step without a synchronisation of their own (``last_status``)."""
 
     def __init__(self, device: torch.device, max_rows: int) -> None:
         self.device = device
-        self.ids = torch.zeros(max_rows, dtype=torch.int32, device=device)
-        self.host_ids = [torch.zeros(max_rows, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self.max_rows = max_rows
+        self._buffer = torch.zeros(max_rows + 1, dtype=torch.int32, device=device)
+        self.status = self._buffer[:1]
+        self.ids = self._buffer[1:]
+        self.host_ids = [torch.zeros(max_rows + 1, dtype=torch.int32).pin_memory()
+                         for _ in range(2)]
         self._done = [torch.cuda.Event(), torch.cuda.Event()]
         self._turn = 0
         self._last = (0, 0)
+        self.last_status = 0
 
     def launch(self, logits: torch.Tensor,
                arrays: "dict[str, torch.Tensor] | None") -> "tuple[int, int]":
@@ -50,10 +60,8 @@ class Sampler:
         self._last = (turn, rows)
         if rows == 0:
             return self._last
-        if rows > self.ids.shape[0]:
-            self.ids = torch.zeros(2 * rows, dtype=torch.int32, device=self.device)
-        if rows > self.host_ids[turn].shape[0]:
-            self.host_ids[turn] = torch.zeros(2 * rows, dtype=torch.int32).pin_memory()
+        if rows > self.max_rows:
+            raise ValueError(f"the sampler was made for {self.max_rows} rows a step, got {rows}")
         out = self.ids[:rows]
         if arrays and "sampling/temperature" in arrays:
             ops.sample_rows(logits, out, arrays["sampling/temperature"].view(torch.float32),
@@ -61,7 +69,7 @@ class Sampler:
                             arrays["sampling/position"])
         else:
             ops.sample_rows(logits, out)
-        self.host_ids[turn][:rows].copy_(out, non_blocking=True)
+        self.host_ids[turn][: rows + 1].copy_(self._buffer[: rows + 1], non_blocking=True)
         self._done[turn].record()
         return self._last
 
@@ -71,7 +79,9 @@ class Sampler:
         if rows == 0:
             return []
         self._done[turn].synchronize()
-        return self.host_ids[turn][:rows].tolist()
+        values = self.host_ids[turn][: rows + 1].tolist()
+        self.last_status = values[0]
+        return values[1:]
 
     def sample(self, logits: torch.Tensor, arrays: "dict[str, torch.Tensor] | None") -> list[int]:
         """Token ids for the rows of ``logits`` [R, V]; synchronises to bring them to the host."""

@@ -5,6 +5,8 @@ import pytest
 
 from distengine_b200.kernels.attention_plan import build_plan, choose_chunk, choose_decode_split
 
+SMS = 148          # the planners are told the device's number of SMs; the tests plan for this many
+
 
 def _covered(items, group, rows_per_tile):
     """(seq, row) -> sorted list of key ranges, from the items of a plan."""
@@ -22,7 +24,7 @@ def test_every_row_tile_gets_its_keys_exactly_once(window, chunk, cap):
     qlen = np.array([130, 1, 1, 21, 2], dtype=np.int32)
     pos0 = np.array([0, 0, 76, 279, 31], dtype=np.int32)
     group, kv_heads, rows = 3, 2, 16
-    plan = build_plan(qlen, pos0, group, kv_heads, rows, window, chunk, cap)
+    plan = build_plan(qlen, pos0, group, kv_heads, rows, window, chunk, cap, sm_count=SMS)
     ranges = _covered(plan.items, group, rows)
     for seq in range(len(qlen)):
         rows_total = int(qlen[seq]) * group
@@ -67,10 +69,10 @@ def test_capped_plan_refuses_a_range_that_needs_more_chunks():
                                                  (1, 1, 1), (3, 5, 100000)])
 @pytest.mark.parametrize("per_sm", [4, 3, 2])
 def test_decode_split_covers_the_span_with_whole_tiles_of_keys(tiles, kv_heads, span, per_sm):
-    cluster, clusters, chunk = choose_decode_split(tiles, kv_heads, span, per_sm=per_sm)
+    cluster, clusters, chunk = choose_decode_split(tiles, kv_heads, span, per_sm=per_sm, sm_count=SMS)
     assert 1 <= cluster <= 8 and clusters >= 1
     # one round of blocks over the SMs, unless even single blocks do not fit in one
-    assert cluster == 1 or tiles * kv_heads * cluster <= per_sm * 148
+    assert cluster == 1 or tiles * kv_heads * cluster <= per_sm * SMS
     assert chunk % 64 == 0 and chunk >= 64
     assert cluster * clusters * chunk >= span                # every key has an item
     assert chunk <= 2048 + 63                                # no block walks more than that
@@ -80,14 +82,14 @@ def test_decode_split_covers_the_span_with_whole_tiles_of_keys(tiles, kv_heads, 
 
 def test_decode_split_takes_sizes_between_the_powers_of_two():
     # 64 tiles of one kv head each... 8 kv heads, three blocks an SM: 6 blocks a cluster fit, 8 not
-    assert choose_decode_split(8, 8, 4096, per_sm=3)[0] == 6
-    assert choose_decode_split(8, 8, 4096, per_sm=4)[0] == 8
-    assert choose_decode_split(8, 4, 520, per_sm=4)[0] == 8
-    assert choose_decode_split(64, 4, 520, per_sm=4)[0] == 2
-    assert choose_decode_split(20, 4, 520, per_sm=4)[0] == 4       # short ranges: powers of two
+    assert choose_decode_split(8, 8, 4096, per_sm=3, sm_count=SMS)[0] == 6
+    assert choose_decode_split(8, 8, 4096, per_sm=4, sm_count=SMS)[0] == 8
+    assert choose_decode_split(8, 4, 520, per_sm=4, sm_count=SMS)[0] == 8
+    assert choose_decode_split(64, 4, 520, per_sm=4, sm_count=SMS)[0] == 2
+    assert choose_decode_split(20, 4, 520, per_sm=4, sm_count=SMS)[0] == 4       # short ranges: powers of two
 
 
 def test_chunk_choice_fills_the_gpu_or_leaves_ranges_whole():
-    assert choose_chunk(1000, 4, 4096) == 0                  # enough tiles: no split
-    c = choose_chunk(8, 4, 4096)
-    assert c in (2048, 1024, 512, 256, 128, 64) and 8 * 4 * -(-4096 // c) >= 296
+    assert choose_chunk(1000, 4, 4096, sm_count=SMS) == 0                  # enough tiles: no split
+    c = choose_chunk(8, 4, 4096, sm_count=SMS)
+    assert c in (2048, 1024, 512, 256, 128, 64) and 8 * 4 * -(-4096 // c) >= 2 * SMS

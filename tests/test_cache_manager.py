@@ -68,24 +68,100 @@ def test_errors_follow_the_reference_classes():
         m.commit("a", -1)
 
 
-def test_rewind_takes_a_length_back_and_keeps_the_pages():
-    """A step that was launched ahead and is not used: the length goes back, the pages stay, and
-    the same tokens can be reserved and committed again."""
+def test_a_tentative_step_is_taken_back_or_confirmed():
+    """A step that was launched ahead: taken back, the length is what it was, the pages stay, and
+    the same tokens can be reserved and committed again; confirmed, it counts like any other."""
     m = manager()
     m.admit("a")
+    m.reserve([("a", 8)])
+    m.commit("a", 8)
     m.reserve([("a", 9)])
-    m.commit("a", 9)
+    m.commit("a", 9, tentative=True)
     free = m.num_free_pages()
-    m.rewind("a", 8)
+    assert m.length("a") == 9
+    with pytest.raises(ValueError):
+        m.commit("a", 10)                                   # not while a step is undecided
+    m.rewind("a")
     assert m.length("a") == 8 and m.num_free_pages() == free
     assert m.pages_needed("a", 9) == 0                      # the page of token 9 is still held
-    m.reserve([("a", 9)])
-    m.commit("a", 9)
     with pytest.raises(ValueError):
-        m.rewind("a", 10)
+        m.rewind("a")                                       # nothing tentative is left
+    m.reserve([("a", 9)])
+    m.commit("a", 9, tentative=True)
+    m.confirm("a")
+    m.confirm("a")                                          # harmless when nothing is pending
+    assert m.length("a") == 9
+    m.reserve([("a", 10)])
+    m.commit("a", 10)
     m.check_invariants()
     m.release("a")
     assert m.num_free_pages() == m.num_pages
+
+
+@pytest.mark.parametrize("length", range(8, 40))
+def test_a_window_keeps_its_pages_until_a_tentative_step_is_confirmed(length):
+    """With page 4 and window 6, a step to ``length + 1`` passes a page whenever
+    (length - 4) % 4 == 0.  Launched ahead, it must not give that page back: taken back, the token
+    at ``length`` is fed again and still reads key ``length - 5``."""
+    page, window = 4, 6
+    m = manager(specs=[PagedKVSpec(2, 16, window)], page=page, pages=16)
+    m.admit("a")
+    m.reserve([("a", length)])
+    m.commit("a", length)
+    first_key = max(0, length - window + 1)
+    m.reserve([("a", length + 1)])
+    m.commit("a", length + 1, tentative=True)
+    table = m.paged[0].tables["a"]
+    assert all(table[p] >= 0 for p in range(first_key // page, length // page + 1))
+    m.rewind("a")
+    assert m.pages_needed("a", length + 1) == 0
+    m.reserve([("a", length + 1)])
+    assert all(table[p] >= 0 for p in range(first_key // page, length // page + 1))
+    m.commit("a", length + 1, tentative=True)
+    m.confirm("a")
+    lo = max(0, length + 1 - window + 1) // page             # now the passed pages are back
+    assert all(p < 0 for p in table[:lo]) and all(p >= 0 for p in table[lo:])
+    m.check_invariants()
+    m.release("a")
+    assert m.num_free_pages() == m.num_pages
+
+
+def test_a_window_page_that_is_gone_is_seen_as_missing():
+    """The quick answer of ``pages_needed`` (the new positions lie in a held page) must not hide a
+    window's first page that is not held."""
+    m = manager(specs=[PagedKVSpec(2, 16, 6)], page=4, pages=16)
+    m.admit("a")
+    m.reserve([("a", 13)])
+    m.commit("a", 13)                                   # keys from 8 on are needed: page 2 on
+    group = m.paged[0]
+    table = group.tables["a"]
+    lost = table[2]
+    m._give(group, [lost])                              # as if a commit had gone one step too far
+    table[2] = -1
+    group.host_table[m.slot("a"), 2] = -1
+    assert m.pages_needed("a", 14) == 1
+
+
+def test_state_rows_come_back_when_a_tentative_step_is_taken_back():
+    m = manager(specs=[FULL, StateSpec((3,))])
+    state = m.bindings()[1].state
+    a, b = m.admit("a"), m.admit("b")
+    state[a], state[b] = 1.0, 2.0
+    m.reserve([("a", 1), ("b", 1)])
+    m.save_states(["a", "b"])
+    state[a] += 10.0                                    # what the step launched ahead does
+    state[b] += 10.0
+    m.commit("a", 1, tentative=True)
+    m.commit("b", 1, tentative=True)
+    m.release("b")                                      # b ended meanwhile
+    m.rewind("a")
+    assert torch.all(state[a] == 1.0) and m.length("a") == 0
+    m.reserve([("a", 1)])
+    m.save_states(["a"])
+    state[a] += 5.0
+    m.commit("a", 1, tentative=True)
+    m.confirm("a")
+    assert torch.all(state[a] == 6.0) and m.length("a") == 1
 
 
 def test_reserve_is_all_or_nothing():
@@ -178,9 +254,16 @@ def test_random_orders_of_requests(seed):
                 m.release(victim)
                 del live[victim]
             else:
+                ahead = rng.random() < 0.3               # a step launched ahead of the host
                 for r, n in wanted:
-                    m.commit(r, n)
-                    live[r] = n
+                    m.commit(r, n, tentative=ahead)
+                if ahead and rng.random() < 0.5:
+                    for r, _ in wanted:
+                        m.rewind(r)
+                else:
+                    for r, n in wanted:
+                        m.confirm(r)
+                        live[r] = n
         elif live:
             rid = list(live)[int(rng.integers(len(live)))]
             m.release(rid)

@@ -92,7 +92,8 @@ def _register():
             ffn = PartSpec.of("gated_mlp", width=w, inner=self.get("inner"), activation="silu")
             attn = PartSpec.of("attention", width=w, heads=self.get("heads"),
                                kv_heads=self.get("kv_heads"), head_dim=self.get("head_dim"),
-                               scale=self.get("head_dim") ** -0.5, window=None,
+                               scale=self.get("head_dim") ** -0.5,
+                               window=dict(self.data).get("window"),
                                position=PartSpec.of("rope", rotary_dim=self.get("head_dim"),
                                                     theta=self.get("theta")))
             toy = PartSpec.of("toy_running_mean", width=w)
@@ -145,7 +146,7 @@ def _plain_toy(config, w, ids, dtype):
             kv[entry] = (k, v)
         else:
             k, v = kv[reads]
-        ctx = plain.plain_attention(q, k, v, pos, None, dtype)
+        ctx = plain.plain_attention(q, k, v, pos, config.get("window"), dtype)
         return plain.plain_linear(ctx.reshape(T, nh * d), w[p + "o_proj.weight"], dtype)
 
     def toy(h, p):
@@ -206,3 +207,56 @@ def test_a_plan_that_reads_a_cache_of_another_shape_is_refused():
         arch.build_model(config, torch.float32, "cuda:0").cache_specs()
     with pytest.raises(ValueError, match="does not run before"):
         arch.build_model(resolve(dict(TOY, plan=[[0, 1], [1, -1]]))[1], torch.float32, "cuda:0")
+
+
+def _plain_toy_generate(config, weights, prompt, count):
+    tokens = list(prompt)
+    for _ in range(count):
+        tokens.append(int(_plain_toy(config, weights, tokens, torch.float32)[-1].argmax()))
+    return tokens[len(prompt):]
+
+
+def test_a_step_taken_back_gives_state_and_window_pages_back(model_root):
+    """Through ``Engine``: a windowed attention layer (window 6, pages of 4) and the running-mean
+    layer, three requests, one of which ends on an end-of-sequence token.  The engine has then
+    already launched the next step for all three; that step is void.  The running sums it
+    advanced must be what they were, and the page that its window would have passed must still
+    be there for the token that is fed again.  Every place the end can fall on is tried, so that
+    the others' lengths meet every alignment of window and page.  Freed pages hold NaN."""
+    _register()
+    from distengine_b200 import Engine, EngineConfig
+    from distengine_b200.weights import write_random_model
+    toy = dict(TOY, kinds=["attention", "toy"], plan=[[0, -1], [1, -1]], window=6,
+               max_positions=128)
+    folder = write_random_model(toy, f"{model_root}/toy-window", seed=6, norm_init="uniform")
+    config, weights = plain.load_model_folder(folder)
+    rng = np.random.default_rng(3)
+    prompts = [[int(t) for t in rng.integers(0, 97, size=n)] for n in (9, 14, 5)]
+    alone = [_plain_toy_generate(config, weights, p, 16) for p in prompts]
+    taken_back = 0
+    for cut in range(1, 10):
+        eos = alone[0][cut]
+        if eos in alone[0][:cut]:
+            continue
+        engine = Engine(folder, EngineConfig(dtype="float32", block_size=4, num_blocks=48,
+                                             decode_batch_size=4))
+        engine.cache.poison = True
+        for group in engine.cache.paged:
+            group.k.fill_(float("nan"))
+            group.v.fill_(float("nan"))
+        voided = []
+        take_back = engine._take_back
+        engine._take_back = lambda prepared: (voided.append(1), take_back(prepared))[1]
+        engine.submit("a", prompts[0], 16, eos_token_id=eos)
+        engine.submit("b", prompts[1], 16, eos_token_id=-1)
+        engine.submit("c", prompts[2], 16, eos_token_id=-1)
+        while engine.has_pending():
+            engine.step()
+        records = {r["request_id"]: r for r in engine.drain_completed()}
+        taken_back += len(voided)
+        assert records["a"]["generated_token_ids"] == alone[0][: cut + 1], cut
+        assert records["b"]["generated_token_ids"] == alone[1], cut
+        assert records["c"]["generated_token_ids"] == alone[2], cut
+        engine.cache.check_invariants()
+        assert engine.cache.num_free_pages() == engine.cache.num_pages
+    assert taken_back >= 4

@@ -50,12 +50,12 @@ def test_dtypes_stay_as_stored(tmp_path):
     os.makedirs(tmp_path / "m")
     save_tensors(str(tmp_path / "m" / "model.safetensors"), tensors)
     expected = {k: tuple(v.shape) for k, v in tensors.items()}
-    kept = load_checked(str(tmp_path / "m"), expected, dtype=torch.bfloat16)
+    kept = load_checked(str(tmp_path / "m"), expected, dtype=torch.bfloat16, integer={"d"})
     assert kept["a"].dtype == torch.bfloat16 and torch.equal(kept["a"], tensors["a"])
     assert kept["b"].dtype == torch.float32 and torch.equal(kept["b"], tensors["b"])   # 32-bit stays
     assert kept["c"].dtype == torch.bfloat16
     assert kept["d"].dtype == torch.int32 and kept["d"].tolist() == list(range(6))
-    wide = load_checked(str(tmp_path / "m"), expected, dtype=torch.float32)
+    wide = load_checked(str(tmp_path / "m"), expected, dtype=torch.float32, integer={"d"})
     assert wide["a"].dtype == wide["c"].dtype == torch.float32 and wide["d"].dtype == torch.int32
 
 
@@ -83,6 +83,62 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(model_root, tmp_pat
     for piece in ("missing tensors (2)", "model.norm.weight", "unexpected tensors (1)",
                   "q_proj.bias", "wrong shapes (1)", "expected [32, 64], file has [64, 64]"):
         assert piece in text
+
+
+def test_a_tensor_of_the_wrong_class_of_dtype_is_named(model_root, tmp_path):
+    """Integers or booleans under a matrix's or a norm weight's name are not cast and loaded: the
+    error names them; so is a floating-point tensor where an integer table is expected."""
+    src = tiny_configs.make_folder("tiny_a", model_root)
+    expected, _, optional = _expected(src)
+    handle = SafetensorsFile(os.path.join(src, "model.safetensors"))
+    tensors = {n: handle.tensor(n).clone() for n in handle.names()}
+    tensors["model.layers.0.mlp.down_proj.weight"] = torch.ones(64, 176, dtype=torch.int8)
+    tensors["model.norm.weight"] = torch.ones(64, dtype=torch.bool)
+    dst = tmp_path / "ints"
+    os.makedirs(dst)
+    shutil.copy(os.path.join(src, "config.json"), dst / "config.json")
+    save_tensors(str(dst / "model.safetensors"), tensors)
+    with pytest.raises(WeightMismatchError) as info:
+        load_checked(str(dst), expected, optional, torch.bfloat16)
+    err = info.value
+    assert [name for name, _, _ in err.wrong_dtype] == ["model.layers.0.mlp.down_proj.weight",
+                                                        "model.norm.weight"]
+    assert not err.missing and not err.unexpected and not err.wrong_shape
+    assert "model.norm.weight: expected a floating-point dtype, file has torch.bool" in str(err)
+    with pytest.raises(WeightMismatchError, match="expected an integer dtype"):
+        load_checked(str(dst), expected, optional, torch.bfloat16,
+                     integer={"model.layers.1.mlp.up_proj.weight"})
+
+
+def test_a_folder_of_shards_is_read_through_its_index(model_root, tmp_path):
+    """model.safetensors.index.json names the files; every tensor is found in its shard, a tensor
+    that no shard holds is missing, and a shard's extra tensor is unexpected."""
+    import json
+    src = tiny_configs.make_folder("tiny_a", model_root)
+    expected, _, optional = _expected(src)
+    handle = SafetensorsFile(os.path.join(src, "model.safetensors"))
+    names = handle.names()
+    parts = [names[0::3], names[1::3], names[2::3]]
+    dst = tmp_path / "shards"
+    os.makedirs(dst)
+    weight_map = {}
+    for i, part in enumerate(parts):
+        file = f"model-{i + 1:05d}-of-00003.safetensors"
+        save_tensors(str(dst / file), {n: handle.tensor(n).clone() for n in part})
+        weight_map.update({n: file for n in part})
+    with open(dst / "model.safetensors.index.json", "w") as out:
+        json.dump({"metadata": {}, "weight_map": weight_map}, out)
+    whole = load_checked(src, expected, optional, torch.float32)
+    sharded = load_checked(str(dst), expected, optional, torch.float32)
+    assert set(sharded) == set(whole) and all(torch.equal(sharded[n], whole[n]) for n in whole)
+    # one shard loses a tensor and gains a stranger
+    file = f"model-{2:05d}-of-00003.safetensors"
+    kept = {n: handle.tensor(n).clone() for n in parts[1][1:]}
+    kept["model.stranger"] = torch.zeros(3)
+    save_tensors(str(dst / file), kept)
+    with pytest.raises(WeightMismatchError) as info:
+        load_checked(str(dst), expected, optional, torch.float32)
+    assert info.value.missing == [parts[1][0]] and info.value.unexpected == ["model.stranger"]
 
 
 def test_untied_model_without_output_matrix_is_an_error(model_root, tmp_path):

@@ -39,13 +39,15 @@ def _symbol():
     return fn, lib.de_attn_static_scratch_error
 
 
-def _call(fn, fx, q_list, heads, kv_heads, d, scale, window, chunk, num_partials_override=None):
+def _call(fn, fx, q_list, heads, kv_heads, d, scale, window, chunk, num_partials_override=None,
+          check_free_memory=False):
     from distengine_b200.kernels.attention_plan import build_plan
     dtype = fx.dtype
     qlen = np.array([q.shape[0] for q in q_list], dtype=np.int32)
     pos0 = np.array([n - ql for n, ql in zip(fx.kv_lens, qlen)], dtype=np.int32)
     qstart = (np.cumsum(qlen) - qlen).astype(np.int32)
-    plan = build_plan(qlen, pos0, heads // kv_heads, kv_heads, 8, window or 0, chunk)
+    plan = build_plan(qlen, pos0, heads // kv_heads, kv_heads, 8, window or 0, chunk,
+                      sm_count=torch.cuda.get_device_properties(0).multi_processor_count)
     assert plan.num_partials > 0
     t = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(DEV)
     q = torch.cat([x.reshape(x.shape[0], heads * d) for x in q_list]).to(DEV, dtype).contiguous()
@@ -53,7 +55,10 @@ def _call(fn, fx, q_list, heads, kv_heads, d, scale, window, chunk, num_partials
     k_pages, v_pages, table = fx.to_device()
     arrays = [t(np.array(fx.slots)), t(qstart), t(qlen), t(pos0), t(plan.items), t(plan.combine)]
     torch.cuda.synchronize()
-    before = torch.cuda.memory_allocated()
+    # what the driver reports as free on the device: a cudaMalloc inside the library would show
+    # here (torch's own counters would not see it).  The first call on a device may make the
+    # context load the kernels' code, so the comparison is made on later calls.
+    before = torch.cuda.mem_get_info()[0]
     code = fn(0 if dtype == torch.float32 else 1, q.data_ptr(), q.stride(0), out.data_ptr(),
               out.stride(0), k_pages.data_ptr(), v_pages.data_ptr(), table.data_ptr(),
               table.stride(0), k_pages.shape[0], arrays[0].data_ptr(), arrays[1].data_ptr(),
@@ -63,7 +68,8 @@ def _call(fn, fx, q_list, heads, kv_heads, d, scale, window, chunk, num_partials
               heads, kv_heads, d, fx.page, float(scale), int(window or 0),
               torch.cuda.current_stream().cuda_stream)
     torch.cuda.synchronize()
-    assert torch.cuda.memory_allocated() == before        # torch's allocator was not touched
+    if check_free_memory:
+        assert torch.cuda.mem_get_info()[0] == before     # no device memory was taken
     return code, out.float().cpu()
 
 
@@ -78,7 +84,8 @@ def test_static_scratch_matches_the_ordinary_entry_points_twice(dtype):
         window = None if call == 0 else 90
         chunk = 64 if call == 0 else 128
         q_list = [torch.randn(ql, heads, d, generator=g).to(dtype).float() for ql in (1, 1, 5)]
-        code, got = _call(fn, fx, q_list, heads, kv_heads, d, d ** -0.5, window, chunk)
+        code, got = _call(fn, fx, q_list, heads, kv_heads, d, d ** -0.5, window, chunk,
+                          check_free_memory=call == 1)
         assert code == 0
         # the existing entry points, with scratch from the allocator (the float32 kernel for both
         # dtypes: a head size of 48 is forced onto it by asking for its tile shape)
@@ -112,3 +119,26 @@ def test_static_scratch_refuses_what_does_not_fit():
     # a request that fits clears the message
     code, _ = _call(fn, fx, q, heads, kv_heads, d, d ** -0.5, None, 64)
     assert code == 0 and error().decode() == ""
+
+
+def test_static_scratch_skips_items_beyond_the_slots_it_was_told():
+    """The size check is made with ``num_partials``; a work item that names a slot at or beyond it
+    must not write there (that could lie past the end of the array).  Told one slot fewer than the
+    plan uses, the call leaves the rows of the tile that owns the last slot as they were and
+    computes every other row as before."""
+    fn, _ = _symbol()
+    heads, kv_heads, d = 4, 2, 32
+    dtype = torch.float32
+    fx = PagedFixture([200, 150], kv_heads, d, 16, dtype, DEV, seed=5)
+    g = torch.Generator().manual_seed(2)
+    q_list = [torch.randn(1, heads, d, generator=g) for _ in range(2)]
+    code, whole = _call(fn, fx, q_list, heads, kv_heads, d, d ** -0.5, None, 64)
+    assert code == 0 and torch.isfinite(whole).all()
+    from distengine_b200.kernels.attention_plan import build_plan
+    plan = build_plan(np.array([1, 1], dtype=np.int32), np.array([199, 149], dtype=np.int32),
+                      heads // kv_heads, kv_heads, 8, 0, 64)
+    code, short = _call(fn, fx, q_list, heads, kv_heads, d, d ** -0.5, None, 64,
+                        num_partials_override=plan.num_partials - 1)
+    assert code == 0
+    assert torch.equal(short[0], whole[0])                   # the first sequence's slots all fit
+    assert torch.isnan(short[1]).all()                       # the tile of the last slot: untouched

@@ -34,7 +34,7 @@ TINY_C = dict(
     prompts=(3, 50), max_new_tokens=6, temperature=0.0,
 )
 
-# a shape the persistent decode kernel takes (head size a multiple of 32), grouped-query
+# head size 64, grouped-query, a given head size
 TINY_D = dict(
     config=dict(architectures=["LlamaForCausalLM"], vocab_size=300, hidden_size=192,
                 intermediate_size=328, num_hidden_layers=2, num_attention_heads=6,
