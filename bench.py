@@ -146,6 +146,55 @@ def weight_bytes(model) -> tuple[int, int]:
     return total, params
 
 
+def reference_arm(args, warmup: int, steps: int) -> int:
+    """The unmodified reference on the same shape and workload (``baseline/reference_arm.py``):
+    its own model, block manager and ``ModelRunner.prefill`` / ``decode_batch``, in float32 with
+    TF32 off as it runs on CUDA.  None of this package is on that path."""
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import reference_arm as arm
+    why = arm.available()
+    if why is None:
+        try:
+            import torch
+            if not torch.cuda.is_available():
+                why = "no CUDA device is visible"
+        except ImportError as error:
+            why = f"torch cannot be imported: {error}"
+    if why is not None:
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+        return 0
+    model = dict(MODEL, num_hidden_layers=args.layers)
+    with ClockSampler() as sampler:
+        got = arm.run(model, args.batch, PROMPT, steps, warmup, PREFILL)
+    ms = got["ms_per_step"]
+    print(json.dumps({
+        "metric": "decode tokens/s at batch 8 (TinyLlama-1.1B shape, 512-token prompts, 1 B200)",
+        "value": round(args.batch / ms * 1e3, 1), "unit": "tokens/s", "n_gpus": 1,
+        "steps": steps, "warmup": warmup, "ms_per_step": round(ms, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32",
+        "data": "synthetic", "impl": "reference",
+        "config": {"model": "TinyLlama-1.1B shape, random weights N(0,0.02) seed 0",
+                   "layers": model["num_hidden_layers"], "layers_of_config": 22,
+                   "hidden": model["hidden_size"], "heads": model["num_attention_heads"],
+                   "kv_heads": model["num_key_value_heads"],
+                   "intermediate": model["intermediate_size"], "vocab": model["vocab_size"],
+                   "global_batch": args.batch, "seq_len": PROMPT, "new_tokens": steps,
+                   "page_size": PAGE, "parallelism": "single GPU",
+                   "path": "ModelRunner.prefill + ModelRunner.decode_batch, unmodified",
+                   "dtype_note": "the reference runs float32 with TF32 off on CUDA "
+                                 "(src/distengine/worker.py:427-430); it has no bfloat16 path",
+                   "l2": "inputs larger than L2: 4.1 GB of weights are read every step"},
+        "clocks": sampler.summary(),
+        "e2e": {"value": round(args.batch / got["wall_ms_per_step"] * 1e3, 1),
+                "unit": "tokens/s", "h2d_bytes_per_step": got["h2d_bytes_per_step"],
+                "d2h_bytes_per_step": got["d2h_bytes_per_step"]},
+        "gpu_launches": 0,
+        "prefill": {"value": round(PREFILL / got["prefill_ms"] * 1e3, 1), "tokens": PREFILL,
+                    "ms": round(got["prefill_ms"], 3)},
+        "points": got["points"]}))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -160,15 +209,12 @@ def main() -> int:
     parser.add_argument("--no-graphs", action="store_true")
     args = parser.parse_args()
 
-    if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference does not install offline: its build backend "
-                          "'hatchling' is neither installed nor in the wheelhouse"}))
-        return 0
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not measured")
         return 2
     warmup, steps = max(args.warmup, 3), max(args.steps, 1)
+    if args.impl == "reference":
+        return reference_arm(args, warmup, steps)
 
     import numpy as np
     import torch

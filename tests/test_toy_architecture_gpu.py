@@ -221,8 +221,9 @@ def test_a_step_taken_back_gives_state_and_window_pages_back(model_root):
     layer, three requests, one of which ends on an end-of-sequence token.  The engine has then
     already launched the next step for all three; that step is void.  The running sums it
     advanced must be what they were, and the page that its window would have passed must still
-    be there for the token that is fed again.  Every place the end can fall on is tried, so that
-    the others' lengths meet every alignment of window and page.  Freed pages hold NaN."""
+    be there for the token that is fed again.  The second request's prompt takes eight lengths in
+    turn, so that the void step meets every alignment of window and page.  Freed pages hold
+    NaN."""
     _register()
     from distengine_b200 import Engine, EngineConfig
     from distengine_b200.weights import write_random_model
@@ -231,13 +232,15 @@ def test_a_step_taken_back_gives_state_and_window_pages_back(model_root):
     folder = write_random_model(toy, f"{model_root}/toy-window", seed=6, norm_init="uniform")
     config, weights = plain.load_model_folder(folder)
     rng = np.random.default_rng(3)
-    prompts = [[int(t) for t in rng.integers(0, 97, size=n)] for n in (9, 14, 5)]
-    alone = [_plain_toy_generate(config, weights, p, 16) for p in prompts]
+    first = [int(t) for t in rng.integers(0, 97, size=9)]
+    third = [int(t) for t in rng.integers(0, 97, size=5)]
+    alone_first = _plain_toy_generate(config, weights, first, 8)
+    # the first request ends on a token that it has not produced before
+    cut = max(i for i in range(len(alone_first)) if alone_first[i] not in alone_first[:i])
     taken_back = 0
-    for cut in range(1, 10):
-        eos = alone[0][cut]
-        if eos in alone[0][:cut]:
-            continue
+    for length in range(6, 14):
+        second = [int(t) for t in rng.integers(0, 97, size=length)]
+        alone = [_plain_toy_generate(config, weights, p, 14) for p in (second, third)]
         engine = Engine(folder, EngineConfig(dtype="float32", block_size=4, num_blocks=48,
                                              decode_batch_size=4))
         engine.cache.poison = True
@@ -247,16 +250,16 @@ def test_a_step_taken_back_gives_state_and_window_pages_back(model_root):
         voided = []
         take_back = engine._take_back
         engine._take_back = lambda prepared: (voided.append(1), take_back(prepared))[1]
-        engine.submit("a", prompts[0], 16, eos_token_id=eos)
-        engine.submit("b", prompts[1], 16, eos_token_id=-1)
-        engine.submit("c", prompts[2], 16, eos_token_id=-1)
+        engine.submit("a", first, 14, eos_token_id=alone_first[cut])
+        engine.submit("b", second, 14, eos_token_id=-1)
+        engine.submit("c", third, 14, eos_token_id=-1)
         while engine.has_pending():
             engine.step()
         records = {r["request_id"]: r for r in engine.drain_completed()}
         taken_back += len(voided)
-        assert records["a"]["generated_token_ids"] == alone[0][: cut + 1], cut
-        assert records["b"]["generated_token_ids"] == alone[1], cut
-        assert records["c"]["generated_token_ids"] == alone[2], cut
+        assert records["a"]["generated_token_ids"] == alone_first[: cut + 1], length
+        assert records["b"]["generated_token_ids"] == alone[0], length
+        assert records["c"]["generated_token_ids"] == alone[1], length
         engine.cache.check_invariants()
         assert engine.cache.num_free_pages() == engine.cache.num_pages
-    assert taken_back >= 4
+    assert taken_back == 8
