@@ -62,6 +62,11 @@ class Engine:
         self.requests: dict[str, Request] = {}
         self.steps = 0
         self.tokens_fed = 0
+        # for tests and debugging: called at every launch with [(request id, position)] and the
+        # float32 logits [rows, vocabulary] at those places, which the next step overwrites (copy
+        # them).  A step that is launched ahead and then taken back is reported too; the step
+        # that redoes its positions reports them again.
+        self.on_logits = None
 
     # ------------------------------------------------------------------ the reference's interface
     def submit(self, request_id: str, prompt_token_ids: list[int], max_new_tokens: int,
@@ -131,6 +136,9 @@ class Engine:
         extra = pack_sampling([r.temperature for r in sampling], [r.seed for r in sampling],
                               [r.num_tokens for r in sampling])
         logits = self.runner.launch(self.runner.prepare(entries, extra))
+        if self.on_logits is not None:
+            self.on_logits([(e.request.request_id, e.request.num_computed + len(e.tokens) - 1)
+                            for e in plan.entries if e.sample], logits)
         return plan, self.sampler.launch(logits, self.runner.last_arrays)
 
     @staticmethod
@@ -165,6 +173,8 @@ class Engine:
         # the ids this step feeds are the ones the running step is about to sample
         logits = self.runner.launch(prepared, token_source=self.sampler.ids[: len(running)],
                                     tentative=True)
+        if self.on_logits is not None:
+            self.on_logits([(r.request_id, r.num_tokens) for r in running], logits)
         return prepared, self.sampler.launch(logits, self.runner.last_arrays)
 
     def _take_back(self, prepared) -> None:

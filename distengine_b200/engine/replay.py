@@ -37,8 +37,11 @@ LIVE_REQUESTS = 8          # slots; a trace holds up to four live requests
 
 def build_runner(model_dir: str, dtype: "str | torch.dtype", max_tokens: int,
                  page_size: int = 16, device: str = "cuda:0",
-                 poison_freed_pages: bool = False, use_graphs: bool = False) -> StepRunner:
-    """Model, cache for ``max_tokens`` tokens (in pages of ``page_size``) and the step runner."""
+                 poison_freed_pages: bool = False, use_graphs: bool = False,
+                 live_requests: int = LIVE_REQUESTS) -> StepRunner:
+    """Model, cache for ``max_tokens`` tokens (in pages of ``page_size``) and the step runner.
+    ``use_graphs``: steps of single tokens are replayed as CUDA graphs, as the engine does;
+    ``live_requests``: slots, the most requests that are live at a time."""
     dtype = parse_dtype(dtype)
     model = load_model(model_dir, dtype, device)
     if max_tokens <= 0:
@@ -46,7 +49,7 @@ def build_runner(model_dir: str, dtype: "str | torch.dtype", max_tokens: int,
     num_pages = (max_tokens + page_size - 1) // page_size
     max_len = min(model.config.max_positions, num_pages * page_size)
     cache = CacheManager(model.cache_specs(), [e.reads_cache_of for e in model.plan], page_size,
-                         num_pages, LIVE_REQUESTS, max_len, dtype, model.device,
+                         num_pages, live_requests, max_len, dtype, model.device,
                          poison_freed_pages=poison_freed_pages)
     return StepRunner(model, cache, use_graphs=use_graphs)
 

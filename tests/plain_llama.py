@@ -188,9 +188,10 @@ def plain_decoder_layer(x: torch.Tensor, positions: torch.Tensor, w: dict[str, t
 
 
 def plain_forward(config: dict, w: dict[str, torch.Tensor], token_ids,
-                  act_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+                  act_dtype: torch.dtype = torch.float32, rows=None) -> torch.Tensor:
     """Logits [T, V] in float32 of one whole sequence from position 0
-    (src/models/llama.py:131-191, 206-217).
+    (src/models/llama.py:131-191, 206-217).  ``rows``: only these positions go through the final
+    norm and the output matrix (the result is [len(rows), V]); the reference computes all.
 
     ``tie_word_embeddings`` true and no ``lm_head.weight`` in the file: the embedding table is the
     output matrix (the reference always has a separate ``lm_head.weight``, src/models/llama.py:201).
@@ -201,6 +202,8 @@ def plain_forward(config: dict, w: dict[str, torch.Tensor], token_ids,
     x = plain_embedding(ids, table)
     for layer in range(int(config["num_hidden_layers"])):
         x = plain_decoder_layer(x, positions, w, layer, config, act_dtype)
+    if rows is not None:
+        x = x[torch.as_tensor(rows, dtype=torch.long)]
     x = plain_rmsnorm(x, w["model.norm.weight"], float(config["rms_norm_eps"]), act_dtype)
     head = w.get("lm_head.weight")
     if head is None:

@@ -37,8 +37,9 @@ def _engine(folder, spec, dtype, capacity_tokens=1024, budget=2048, seqs=4):
 
 def _check_against_plain(config, weights, prompt, got, temperature, seed, dtype):
     """Equal tokens; in bfloat16 a different token is accepted only where the plain logits of the
-    two candidates lie closer together than the bfloat16 bound (a near tie), and the comparison
-    ends there since the sequences part."""
+    two candidates lie closer together than the bfloat16 bound (a near tie).  The comparison goes
+    on after such a token: the plain path is always fed the engine's own tokens, so every later
+    token is still checked against the logits of the sequence the engine really has."""
     tokens = list(prompt)
     for i, token in enumerate(got):
         logits = plain.plain_forward(config, weights, tokens, dtype)[-1]
@@ -48,7 +49,6 @@ def _check_against_plain(config, weights, prompt, got, temperature, seed, dtype)
             assert temperature == 0.0
             gap = (logits[want] - logits[token]).item()
             assert 0 <= gap <= BF16_MAX_REL * logits.abs().max().item(), (i, token, want, gap)
-            return
         tokens.append(token)
 
 
