@@ -9,7 +9,11 @@ items on the host and launches them.
   (``csrc/attention_simt.cu``), 8 rows a tile.
 
 Long key ranges of a step with few tiles are cut into chunks; ``de_attn_combine`` merges the
-partial results (``attention_plan``).
+partial results (``attention_plan``).  In float32 the chunk length is fixed (``F32_CHUNK`` keys,
+at absolute multiples of it) whatever else the step holds: a row's keys are then always summed in
+the same order - tiles of 32 keys in ascending order within a chunk, chunks in ascending order -
+so its result does not depend, bit for bit, on how the tokens were cut into steps or on what
+shares the batch.
 """
 
 from __future__ import annotations
@@ -26,6 +30,7 @@ from .attention_plan import build_plan, choose_chunk, choose_decode_split
 from .ops import _check, _i32, _need, _ptr, _stream, _tag
 
 MAX_HEAD_DIM = 256
+F32_CHUNK = 512          # keys in a chunk of the float32 path (a fixed order of summation)
 _status_fallback: "torch.Tensor | None" = None
 NARROW_ROWS = 16
 
@@ -76,6 +81,7 @@ class AttentionLauncher:
         else:
             self.shapes = [_Shape("rows8", 8, -1)]
             self.module = ("attention_simt", ())
+        self.fixed_chunk = F32_CHUNK if dtype == torch.float32 else None
         # steps of decoded tokens only: rotation, cache write, attention and merge in one launch;
         # DISTENGINE_B200_DECODE_ATTENTION=split keeps them apart
         self.fused_decode = (self.tensor_cores and os.environ.get(
@@ -192,6 +198,13 @@ class AttentionLauncher:
             chunk = chunks_cap = None
             if force_chunk is not None:
                 chunk, chunks_cap = force_chunk, force_cap
+            elif self.fixed_chunk is not None:
+                chunk = self.fixed_chunk
+                if prep.graph_shape is not None:
+                    cap = int(prep.graph_shape["context_cap"])
+                    span = cap if not self.window else min(cap, self.window
+                                                           + int(host.seq_qlen.max()))
+                    chunks_cap = (span + chunk - 1) // chunk + (1 if self.window else 0)
             elif prep.graph_shape is not None:
                 cap = int(prep.graph_shape["context_cap"])
                 span = cap if not self.window else min(cap, self.window + int(host.seq_qlen.max()))

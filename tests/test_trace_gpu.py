@@ -142,24 +142,90 @@ def test_trace_run_program(dtype_name, model_root):
         assert_close(got, reference[dtype][rid][pos], dtype, f"trace_run {rid}@{pos}")
 
 
-@pytest.mark.parametrize("dtype_name", ["float32", "bfloat16"])
-def test_cuts_agree_with_each_other(dtype_name, model_root):
-    """Logits at a position do not depend on the cut beyond rounding: in float32 the ways of
-    cutting agree far more closely with each other than the bound against the plain
-    implementation asks."""
+@pytest.mark.parametrize("name", ["tiny_b", "tiny_c"])
+def test_float32_cuts_agree_bit_for_bit(name, model_root):
+    """In float32 the logits at a position are the same bits however the tokens were cut into
+    steps and whatever else was in the batch, with and without CUDA graphs: every kernel of the
+    32-bit path sums a row's terms in an order that depends on the row alone (the matrix product
+    over k in ascending order, the attention over tiles of 32 keys at absolute positions within
+    chunks of a fixed length, chunks in ascending order).  One request is 1,300 tokens long, so
+    that its key ranges span three chunks."""
+    from distengine_b200.engine.replay import build_runner
+    from distengine_b200.kernels.attention import F32_CHUNK
+    from distengine_b200.weights import write_random_model
+    spec = tiny_configs.ALL[name]
+    shape = dict(spec["config"], max_position_embeddings=2048)
+    folder = write_random_model(shape, f"{model_root}/{name}-2048-positions", spec["seed"],
+                                dtype="float32", norm_init=spec["norm_init"])
+    vocab = shape["vocab_size"]
+    requests = {f"r{i}": tiny_configs.prompt_tokens(name, n, i)
+                for i, n in enumerate([70, 2 * F32_CHUNK + 276, 33, 100, 5])}
+    cuts = {
+        "whole": (th.schedule_whole(requests), 1408),
+        "tail": (th.schedule_tail(requests, 32), 1408),
+        "portions": (th.schedule_portions(requests, sizes=(7, 2, 130, 1, 300, 17, 2, 3, 64, 5)),
+                     1408),
+        "mixed": (th.schedule_mixed(requests, 1600, seed=3), 1600),
+    }
+    results = {}
+    for schedule, graphs in (("whole", False), ("tail", False), ("tail", True), ("portions", False),
+                             ("mixed", False), ("mixed", True)):
+        steps, max_tokens = cuts[schedule]
+        runner = build_runner(folder, "float32", max_tokens, page_size=spec["page_size"],
+                              use_graphs=graphs)
+        with tempfile.TemporaryDirectory() as out:
+            th.replay_in_process(runner, steps, out)
+            results[(schedule, graphs)] = th.collect(steps, out, vocab)
+        if graphs:
+            assert runner.graph_replays > 0
+    base = results[("whole", False)]
+    for key, rows in results.items():
+        assert rows
+        for place, got in rows.items():
+            assert np.array_equal(got, base[place]), f"{key} differs from whole at {place}"
+
+
+def test_bfloat16_cuts_agree_with_each_other(model_root):
+    """bfloat16 steps of different shapes take different kernels (tile shapes, products), so the
+    cuts agree within the bfloat16 bound, not bit for bit."""
     from distengine_b200.engine.replay import build_runner
     folder, config, requests, _ = _model("tiny_b", model_root)
     results = {}
     for schedule in ("whole", "tail", "portions", "mixed"):
         steps, max_tokens = _schedules(requests)[schedule]
-        runner = build_runner(folder, dtype_name, max_tokens, page_size=8)
+        runner = build_runner(folder, "bfloat16", max_tokens, page_size=8)
         with tempfile.TemporaryDirectory() as out:
             th.replay_in_process(runner, steps, out)
             results[schedule] = th.collect(steps, out, config["vocab_size"])
     base = results["whole"]
     for schedule, rows in results.items():
         for key, got in rows.items():
-            assert_close(got, base[key], DTYPES[dtype_name], f"{schedule} against whole {key}")
+            assert_close(got, base[key], torch.bfloat16, f"{schedule} against whole {key}")
+
+
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c", "tiny_d", "tiny_e"])
+@pytest.mark.parametrize("dtype_name", ["float32", "bfloat16"])
+@pytest.mark.parametrize("schedule", ["tail", "mixed", "mixed_tight"])
+def test_replay_with_graphs_matches_plain(name, dtype_name, schedule, model_root):
+    """The same traces with steps of single tokens replayed as CUDA graphs, as the engine runs
+    them: graphed and ungraphed decode steps are both under every cut."""
+    from distengine_b200.engine.replay import build_runner
+    folder, config, requests, reference = _model(name, model_root)
+    dtype = DTYPES[dtype_name]
+    steps, max_tokens = _schedules(requests)[schedule]
+    runner = build_runner(folder, dtype_name, max_tokens,
+                          page_size=tiny_configs.ALL[name]["page_size"],
+                          poison_freed_pages=True, use_graphs=True)
+    with tempfile.TemporaryDirectory() as out:
+        th.replay_in_process(runner, steps, out)
+        rows = th.collect(steps, out, config["vocab_size"])
+    assert runner.graph_replays > 0
+    runner.cache.check_invariants()
+    for rid in requests:
+        positions = sorted(p for r, p in rows if r == rid)
+        got = np.stack([rows[(rid, p)] for p in positions])
+        assert_close(got, reference[dtype][rid][positions], dtype,
+                     f"{name} graphs {schedule} {rid}")
 
 
 @pytest.mark.parametrize("name", ["tiny_d", "tiny_e"])
