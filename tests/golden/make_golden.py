@@ -12,6 +12,13 @@ random weights by state-dict name, and run whole and uncached in float32
 ``tie_word_embeddings`` (src/models/llama.py:201), so a tied model gets a copy of the embedding
 table as its ``lm_head.weight``.  Outputs: for every tiny model, token ids and the reference's
 logits at all positions.  ``tests/test_plain.py`` checks the plain implementation against them.
+
+The reference has no bfloat16 mode of its own, but its modules run in whatever dtype their
+parameters have: the same model cast to bfloat16 (weights, activations and the residual sums all
+bfloat16, src/models/llama.py:74-89) is run too and its logits stored as ``logits_bf16``.  The
+engine keeps the residual stream and the logits in float32, so it does not reproduce those
+roundings; the stored logits anchor how far the engine's bfloat16 path, and the plain
+implementation's bfloat16 rounding model, lie from the reference's own arithmetic in that dtype.
 """
 
 from __future__ import annotations
@@ -71,6 +78,15 @@ def main() -> None:
             ids = tiny_configs.prompt_tokens(name, length)
             with torch.inference_mode():
                 ref_logits = model(torch.tensor([ids]))[0].to(torch.float32)
+                bf16_model = LlamaForCausalLM(ref_config).to(torch.bfloat16).eval()
+                bf16_model.load_state_dict({k: v.to(torch.bfloat16) for k, v in state.items()},
+                                           strict=True)
+                ref_bf16 = bf16_model(torch.tensor([ids]))[0].to(torch.float32)
+            plain_bf16 = plain_llama.plain_forward(config, weights, ids, torch.bfloat16)
+            err16 = (plain_bf16 - ref_bf16).abs()
+            print(f"{name}: bfloat16 rounding model against the reference cast to bfloat16: max "
+                  f"{err16.max().item():.3e}, rms {err16.pow(2).mean().sqrt().item():.3e} "
+                  f"(max |logit| {ref_bf16.abs().max().item():.3e})")
             plain = plain_llama.plain_forward(config, weights, ids)
             err = (plain - ref_logits).abs().max().item()
             scale = ref_logits.abs().max().item()
@@ -79,7 +95,7 @@ def main() -> None:
             assert err <= 2e-6 * max(1.0, scale), "the plain implementation disagrees"
             np.savez_compressed(os.path.join(HERE, f"{name}.npz"),
                                 token_ids=np.asarray(ids, dtype=np.int32),
-                                logits=ref_logits.numpy())
+                                logits=ref_logits.numpy(), logits_bf16=ref_bf16.numpy())
 
 
 if __name__ == "__main__":

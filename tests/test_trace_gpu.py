@@ -185,6 +185,29 @@ def test_float32_cuts_agree_bit_for_bit(name, model_root):
             assert np.array_equal(got, base[place]), f"{key} differs from whole at {place}"
 
 
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+def test_bfloat16_engine_against_the_reference_run_in_bfloat16(name, model_root):
+    """Anchors the bfloat16 path on the reference itself and not only on the plain
+    implementation's rounding model: the logits that the reference's own modules gave when cast
+    to bfloat16 on the CPU (tests/golden, made by make_golden.py) against the engine's, for the
+    sequence whole and with its last 32 tokens fed one by one.  The engine adds the residual
+    stream in float32 where the reference adds in bfloat16; the bound is the bfloat16 bound."""
+    from distengine_b200.engine.replay import build_runner
+    folder = tiny_configs.make_folder(name, model_root, dtype="float32")
+    golden = np.load(os.path.join(ROOT, "tests", "golden", f"{name}.npz"))
+    ids = [int(t) for t in golden["token_ids"]]
+    requests = {"g": ids}
+    for steps in (th.schedule_whole(requests), th.schedule_tail(requests, 32)):
+        runner = build_runner(folder, "bfloat16", 128,
+                              page_size=tiny_configs.ALL[name]["page_size"])
+        with tempfile.TemporaryDirectory() as out:
+            th.replay_in_process(runner, steps, out)
+            rows = th.collect(steps, out, golden["logits"].shape[1])
+        got = np.stack([rows[("g", p)] for p in range(len(ids))])
+        assert_close(got, golden["logits_bf16"], torch.bfloat16, f"{name} against the reference "
+                     "in bfloat16")
+
+
 def test_bfloat16_cuts_agree_with_each_other(model_root):
     """bfloat16 steps of different shapes take different kernels (tile shapes, products), so the
     cuts agree within the bfloat16 bound, not bit for bit."""
