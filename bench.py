@@ -1,19 +1,32 @@
-"""Decode and prefill throughput of the engine on one B200, TinyLlama-1.1B layer sizes, random
-weights, bfloat16.
+"""Decode and prefill throughput of the engine on one B200, random weights.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload headline|mixed|long|fp32] [--layers L]
 
-A step is one decode step of a batch of 8 requests whose prompts of 512 tokens are in the cache;
-K steps are timed with CUDA events after W warm-up steps.  One JSON line is printed:
+The default (``headline``) has the TinyLlama-1.1B layer sizes in bfloat16.  A step is one decode
+step of a batch of 8 requests whose prompts of 512 tokens are in the cache; K steps are timed with
+CUDA events after W warm-up steps.  One JSON line is printed:
 
 * ``value``: decoded tokens a second of the step function fed from the host with fixed tokens (no
   read-back between steps);
 * ``e2e``: the same through the Python entry point (``Engine.submit`` / ``Engine.step``): every
-  step uploads its arrays from pinned host memory and reads the sampled tokens back;
+  step uploads its arrays from pinned host memory and reads the sampled tokens back; timed with
+  the host's clock over at least 128 steps, whatever K is (a few steps are too short a stretch
+  for the host's clock);
 * ``prefill``: one prompt of 2,048 tokens in one step;
 * ``roofline``: bytes a decode step has to read (every weight once, the live requests' cache)
   over its time, against the measured copy bandwidth;
 * ``points``: decode at batch 1 and 64.
+
+Other workloads, each with its own line (the number of layers is named beside the model's):
+
+* ``mixed``: Llama-2-7B layer sizes, 32 requests with prompts of 64 to 2,048 tokens and 256 new
+  tokens each through ``Engine`` with a budget of 512 tokens a step (prompt portions beside
+  decoded tokens); generated tokens a second end to end, and the sum of the steps' roofline times
+  (the slower of flops at the matrix peak and bytes at copy bandwidth) over the time taken.
+* ``long``: Llama-3-8B layer sizes (vocabulary 128,256), 64 requests with prompts of 4,096 tokens:
+  prompt portions of 4,096 tokens and decode steps at batch 64 over the long cache.
+* ``fp32``: the headline's sizes in the true 32-bit path (decode at batch 8, prefill of 2,048).
 """
 
 from __future__ import annotations
@@ -36,6 +49,15 @@ MODEL = dict(architectures=["LlamaForCausalLM"], vocab_size=32000, hidden_size=2
              intermediate_size=5632, num_hidden_layers=22, num_attention_heads=32,
              num_key_value_heads=4, rms_norm_eps=1e-5, rope_theta=10000.0,
              max_position_embeddings=2048, tie_word_embeddings=False)
+# BASELINE.json configs[3] and [4]
+LLAMA2_7B = dict(architectures=["LlamaForCausalLM"], vocab_size=32000, hidden_size=4096,
+                 intermediate_size=11008, num_hidden_layers=32, num_attention_heads=32,
+                 num_key_value_heads=32, rms_norm_eps=1e-5, rope_theta=10000.0,
+                 max_position_embeddings=4096, tie_word_embeddings=False)
+LLAMA3_8B = dict(architectures=["LlamaForCausalLM"], vocab_size=128256, hidden_size=4096,
+                 intermediate_size=14336, num_hidden_layers=32, num_attention_heads=32,
+                 num_key_value_heads=8, rms_norm_eps=1e-5, rope_theta=500000.0,
+                 max_position_embeddings=8192, tie_word_embeddings=False)
 PROMPT, NEW_TOKENS, PREFILL, PAGE = 512, 128, 2048, 16
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
@@ -117,16 +139,19 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def model_folder(layers: int) -> str:
+def model_folder(layers: int, shape: "dict | None" = None, name: str = "tinyllama") -> str:
     """The random-weights model folder (written once per machine into the temporary folder)."""
     from distengine_b200.weights import write_random_model
-    MODEL["num_hidden_layers"] = layers
+    if shape is None:
+        MODEL["num_hidden_layers"] = layers
+        shape = MODEL
+    shape = dict(shape, num_hidden_layers=layers)
     folder = os.path.join(tempfile.gettempdir(), f"distengine_b200-bench-{os.getuid()}",
-                          f"tinyllama-shape-{layers}-layers-seed0-bf16")
+                          f"{name}-shape-{layers}-layers-seed0-bf16")
     marker = os.path.join(folder, ".complete")
     if not os.path.isfile(marker):
         print("[bench] writing the random-weights model folder ...", file=sys.stderr, flush=True)
-        write_random_model(MODEL, folder, seed=0, dtype="bfloat16")
+        write_random_model(shape, folder, seed=0, dtype="bfloat16")
         with open(marker, "w") as handle:
             handle.write("ok")
     return folder
@@ -195,6 +220,238 @@ def reference_arm(args, warmup: int, steps: int) -> int:
     return 0
 
 
+def kv_bytes_per_token(engine) -> int:
+    return sum(2 * g.k.shape[0] * g.spec.kv_heads * g.spec.head_dim * g.k.element_size()
+               for g in engine.cache.paged)
+
+
+def shape_config(shape: dict, layers: int, name: str, extra: dict) -> dict:
+    """The flat ``config`` entry of a record: every size, both layer counts."""
+    out = {"model": f"{name} shape, random weights N(0,0.02) seed 0", "layers": layers,
+           "layers_of_config": shape["num_hidden_layers"], "hidden": shape["hidden_size"],
+           "heads": shape["num_attention_heads"], "kv_heads": shape["num_key_value_heads"],
+           "head_dim": shape["hidden_size"] // shape["num_attention_heads"],
+           "intermediate": shape["intermediate_size"], "vocab": shape["vocab_size"],
+           "page_size": PAGE, "parallelism": "single GPU"}
+    out.update(extra)
+    return out
+
+
+def timed_decode(engine, batch: int, prompt: int, k_steps: int, w_steps: int, rng, vocab: int,
+                 portion: int = 2048):
+    """Device-timed decode steps of ``batch`` requests whose prompts are in the cache, fed from
+    the host with fixed tokens.  Returns (ms a step, launches, mean context, clocks)."""
+    import torch
+    from distengine_b200.engine.step import StepEntry
+    from distengine_b200.kernels import ops
+    runner = engine.runner
+    ids = [f"d{batch}-{i}" for i in range(batch)]
+    for rid in ids:                                       # prompts into the cache
+        left = [int(t) for t in rng.integers(0, vocab, size=prompt)]
+        while left:
+            runner.step([StepEntry(rid, left[:portion], [])])
+            left = left[portion:]
+    feed = [[StepEntry(rid, [int(t)], [0]) for rid, t in zip(ids, row)]
+            for row in rng.integers(0, vocab, size=(w_steps + k_steps, batch))]
+    for entries in feed[:w_steps]:
+        ops.sample_rows(runner.step(entries), engine.sampler.ids[:batch])
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    launches = ops.launch_count
+    with ClockSampler() as sampler:
+        start.record()
+        for entries in feed[w_steps:]:
+            ops.sample_rows(runner.step(entries), engine.sampler.ids[:batch])
+        stop.record()
+        torch.cuda.synchronize()
+    ms = start.elapsed_time(stop) / k_steps
+    launches = ops.launch_count - launches
+    context = prompt + w_steps + (k_steps - 1) / 2 + 1
+    for rid in ids:
+        runner.release(rid)
+    runner.check_status()
+    return ms, launches, context, sampler.summary()
+
+
+def timed_prefill(engine, length: int, rng, vocab: int, repeats: int = 5) -> float:
+    """Median milliseconds of one prompt of ``length`` tokens in one step."""
+    import torch
+    from distengine_b200.engine.step import StepEntry
+    runner = engine.runner
+
+    def once():
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        entry = StepEntry("prefill", [int(t) for t in rng.integers(0, vocab, size=length)],
+                          [length - 1])
+        torch.cuda.synchronize()
+        start.record()
+        runner.step([entry])
+        stop.record()
+        torch.cuda.synchronize()
+        runner.release("prefill")
+        return start.elapsed_time(stop)
+
+    for _ in range(3):
+        once()
+    return statistics.median(once() for _ in range(repeats))
+
+
+def prefill_flops(shape: dict, layers: int, layer_params: int, length: int, start: int = 0) -> int:
+    """Flops of a prompt portion of ``length`` tokens that begins at position ``start``."""
+    heads = shape["num_attention_heads"]
+    head_dim = shape["hidden_size"] // heads
+    keys = length * start + length * (length + 1) // 2
+    return (2 * length * layer_params + 4 * head_dim * heads * keys * layers
+            + 2 * shape["vocab_size"] * shape["hidden_size"])
+
+
+def workload_fp32(args, warmup: int, steps: int) -> int:
+    """The headline's sizes in the true 32-bit path: float32 weights, cache and activations, the
+    FFMA matrix product and the CUDA-core attention, no tensor cores."""
+    import numpy as np
+    from distengine_b200 import Engine, EngineConfig
+    peak, peak_kind = peaks()
+    folder = model_folder(args.layers)
+    rng = np.random.default_rng(0)
+    vocab = MODEL["vocab_size"]
+    pages = (args.batch * (PROMPT + 8 + warmup + steps) + PREFILL) // PAGE + 64
+    engine = Engine(folder, EngineConfig(dtype="float32", block_size=PAGE, num_blocks=pages,
+                                         decode_batch_size=max(args.batch, 8),
+                                         max_batch_tokens=PREFILL,
+                                         use_graphs=not args.no_graphs))
+    w_bytes, layer_params = weight_bytes(engine.model)
+    prefill_ms = timed_prefill(engine, PREFILL, rng, vocab, repeats=3)
+    ms, launches, context, clocks = timed_decode(engine, args.batch, PROMPT, steps, warmup, rng,
+                                                 vocab)
+    step_bytes = w_bytes + args.batch * context * kv_bytes_per_token(engine)
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    flops = prefill_flops(MODEL, args.layers, layer_params, PREFILL)
+    print(json.dumps({
+        "metric": "decode tokens/s at batch 8, true float32 path (TinyLlama-1.1B shape)",
+        "value": round(args.batch / ms * 1e3, 1), "unit": "tokens/s", "n_gpus": 1,
+        "steps": steps, "warmup": warmup, "ms_per_step": round(ms, 4), "dtype": "fp32",
+        "higher_is_better": True, "data": "synthetic", "impl": "ours", "workload": "fp32",
+        "config": shape_config(MODEL, args.layers, "TinyLlama-1.1B", {
+            "global_batch": args.batch, "seq_len": PROMPT, "peaks": peak_kind,
+            "matrix_mode": "IEEE float32 FFMA, no TF32"}),
+        "clocks": clocks, "gpu_launches": int(launches),
+        "prefill": {"value": round(PREFILL / prefill_ms * 1e3, 1), "tokens": PREFILL,
+                    "ms": round(prefill_ms, 3), "tflops": round(flops / prefill_ms / 1e9, 2)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"],
+                     "unit": "GB/s", "frac": round(achieved / peak["hbm_gbs"], 4)}}))
+    return 0
+
+
+def workload_long(args, warmup: int, steps: int) -> int:
+    """Llama-3-8B layer sizes: 64 requests with prompts of 4,096 tokens (fed as portions of 4,096
+    tokens), then decode steps at batch 64 over the long cache; vocabulary 128,256."""
+    import numpy as np
+    from distengine_b200 import Engine, EngineConfig
+    peak, peak_kind = peaks()
+    shape, prompt, batch = LLAMA3_8B, 4096, 64
+    folder = model_folder(args.layers, shape, "llama3-8b")
+    rng = np.random.default_rng(0)
+    vocab = shape["vocab_size"]
+    pages = batch * (prompt + 16 + warmup + steps) // PAGE + 64
+    engine = Engine(folder, EngineConfig(dtype="bfloat16", block_size=PAGE, num_blocks=pages,
+                                         decode_batch_size=batch, max_batch_tokens=prompt,
+                                         use_graphs=not args.no_graphs))
+    w_bytes, layer_params = weight_bytes(engine.model)
+    prefill_ms = timed_prefill(engine, prompt, rng, vocab, repeats=3)
+    ms, launches, context, clocks = timed_decode(engine, batch, prompt, steps, warmup, rng, vocab,
+                                                 portion=prompt)
+    step_bytes = w_bytes + batch * context * kv_bytes_per_token(engine)
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    flops = prefill_flops(shape, args.layers, layer_params, prompt)
+    print(json.dumps({
+        "metric": "decode tokens/s at batch 64 over 4,096-token prompts (Llama-3-8B shape)",
+        "value": round(batch / ms * 1e3, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps,
+        "warmup": warmup, "ms_per_step": round(ms, 4), "dtype": "bf16",
+        "higher_is_better": True, "data": "synthetic", "impl": "ours", "workload": "long",
+        "config": shape_config(shape, args.layers, "Llama-3-8B", {
+            "global_batch": batch, "seq_len": prompt, "peaks": peak_kind,
+            "cuda_graphs": bool(engine.runner.graph_replays)}),
+        "clocks": clocks, "gpu_launches": int(launches),
+        "prefill": {"value": round(prompt / prefill_ms * 1e3, 1), "tokens": prompt,
+                    "ms": round(prefill_ms, 3),
+                    "frac": round(flops / (prefill_ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"],
+                     "unit": "GB/s", "frac": round(achieved / peak["hbm_gbs"], 4)}}))
+    return 0
+
+
+def workload_mixed(args, warmup: int, steps: int) -> int:
+    """Llama-2-7B layer sizes through ``Engine``: 32 requests, prompts of 64 to 2,048 tokens, 256
+    new tokens each, a budget of 512 tokens a step, so most steps hold a prompt portion beside
+    decoded tokens.  Timed with the host's clock from the first submit to the last completion
+    (the second of two identical runs; the first compiles, sizes buffers and captures graphs)."""
+    import numpy as np
+    import torch
+    from distengine_b200 import Engine, EngineConfig
+    peak, peak_kind = peaks()
+    shape, requests, new_tokens, budget = LLAMA2_7B, 32, 256, 512
+    folder = model_folder(args.layers, shape, "llama2-7b")
+    rng = np.random.default_rng(0)
+    vocab = shape["vocab_size"]
+    lengths = [int(n) for n in rng.integers(64, 2049, size=requests)]
+    prompts = [[int(t) for t in rng.integers(0, vocab, size=n)] for n in lengths]
+    pages = sum(n + new_tokens + PAGE for n in lengths) // PAGE + 64
+    engine = Engine(folder, EngineConfig(dtype="bfloat16", block_size=PAGE, num_blocks=pages,
+                                         decode_batch_size=requests, max_batch_tokens=budget,
+                                         use_graphs=not args.no_graphs))
+    w_bytes, layer_params = weight_bytes(engine.model)
+    kv_token = kv_bytes_per_token(engine)
+    heads, head_dim = shape["num_attention_heads"], shape["hidden_size"] // shape["num_attention_heads"]
+
+    def run(tag):
+        for i, prompt in enumerate(prompts):
+            engine.submit(f"{tag}-{i}", prompt, new_tokens, -1)
+        ideal, n_steps, fed_before = 0.0, 0, engine.tokens_fed
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        while engine.has_pending():
+            held = sum(live.length for live in engine.cache.live.values())
+            before = engine.tokens_fed
+            engine.step()
+            fed = engine.tokens_fed - before
+            if fed == 0:
+                continue
+            n_steps += 1
+            # the step's roofline time: every weight once and the live cache against copy
+            # bandwidth, or its flops against the matrix peak, whichever is slower
+            flops = 2 * fed * layer_params + 4 * head_dim * heads * held * args.layers
+            ideal += max((w_bytes + held * kv_token) / (peak["hbm_gbs"] * 1e9),
+                         flops / (peak["bf16_tflops"] * 1e12))
+        torch.cuda.synchronize()
+        return time.perf_counter() - t0, ideal, n_steps, engine.tokens_fed - fed_before
+
+    run("warm")
+    engine.drain_completed()
+    with ClockSampler() as sampler:
+        seconds, ideal, n_steps, fed = run("timed")
+    done = engine.drain_completed()
+    assert len(done) == requests and all(len(r["generated_token_ids"]) == new_tokens for r in done)
+    generated = requests * new_tokens
+    print(json.dumps({
+        "metric": "generated tokens/s end to end, 32 requests, chunked prefill of 512 tokens a "
+                  "step (Llama-2-7B shape)",
+        "value": round(generated / seconds, 1), "unit": "tokens/s", "n_gpus": 1,
+        "steps": n_steps, "warmup": n_steps, "ms_per_step": round(seconds / n_steps * 1e3, 4),
+        "dtype": "bf16", "higher_is_better": True, "data": "synthetic", "impl": "ours",
+        "workload": "mixed",
+        "config": shape_config(shape, args.layers, "Llama-2-7B", {
+            "requests": requests, "prompt_tokens": sum(lengths), "new_tokens": new_tokens,
+            "token_budget": budget, "peaks": peak_kind,
+            "cuda_graphs": bool(engine.runner.graph_replays),
+            "preemptions": engine.scheduler.num_preemptions}),
+        "clocks": sampler.summary(),
+        "tokens_fed_per_s": round(fed / seconds, 1),
+        "roofline": {"bound": "per step: hbm or tensor, whichever is slower",
+                     "ideal_s": round(ideal, 4), "seconds": round(seconds, 4),
+                     "frac": round(ideal / seconds, 4)}}))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -207,7 +464,11 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=MODEL["num_hidden_layers"],
                         help="fewer layers than the configuration's 22, for small profiling runs")
     parser.add_argument("--no-graphs", action="store_true")
+    parser.add_argument("--workload", default="headline",
+                        choices=["headline", "mixed", "long", "fp32"])
     args = parser.parse_args()
+    if args.workload in ("mixed", "long") and "--layers" not in " ".join(sys.argv):
+        args.layers = 8          # of the 32 that the Llama-2-7B and Llama-3-8B shapes have
 
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not measured")
@@ -215,6 +476,9 @@ def main() -> int:
     warmup, steps = max(args.warmup, 3), max(args.steps, 1)
     if args.impl == "reference":
         return reference_arm(args, warmup, steps)
+    if args.workload != "headline":
+        return {"mixed": workload_mixed, "long": workload_long,
+                "fp32": workload_fp32}[args.workload](args, warmup, steps)
 
     import numpy as np
     import torch
@@ -314,15 +578,16 @@ def main() -> int:
         points[f"decode_b{b}"] = round(b / b_ms * 1e3, 1)
 
     # ------------------------------------------------------------------ end to end
+    e2e_steps = max(steps, 128)
     for i in range(args.batch):
-        engine.submit(f"e2e-{i}", tokens(PROMPT), warmup + steps + 1, -1)
+        engine.submit(f"e2e-{i}", tokens(PROMPT), warmup + e2e_steps + 1, -1)
     while any(r.num_computed < PROMPT for r in engine.requests.values()) or engine.steps == 0:
         engine.step()
     for _ in range(warmup):
         engine.step()
     torch.cuda.synchronize()
     t0 = time.perf_counter()
-    for _ in range(steps):
+    for _ in range(e2e_steps):
         engine.step()
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
@@ -347,8 +612,9 @@ def main() -> int:
                    "l2": "inputs larger than L2: 2.07 GB of weights are read every step",
                    "peaks": peak_kind},
         "clocks": clocks,
-        "e2e": {"value": round(args.batch * steps / e2e_s, 1), "unit": "tokens/s",
-                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": 4 * args.batch},
+        "e2e": {"value": round(args.batch * e2e_steps / e2e_s, 1), "unit": "tokens/s",
+                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": 4 * (args.batch + 1),
+                "steps": e2e_steps},
         "gpu_launches": int(launches),
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"],
