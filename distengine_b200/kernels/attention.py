@@ -30,7 +30,7 @@ from .attention_plan import build_plan, choose_chunk, choose_decode_split
 from .ops import _check, _i32, _need, _ptr, _stream, _tag
 
 MAX_HEAD_DIM = 256
-F32_CHUNK = 512          # keys in a chunk of the float32 path (a fixed order of summation)
+F32_CHUNK = 128          # keys in a chunk of the float32 path (a fixed order of summation)
 _status_fallback: "torch.Tensor | None" = None
 NARROW_ROWS = 16
 

@@ -30,7 +30,7 @@ SIGNATURES: dict[str, dict[str, list]] = {
         "de_sample_rows": [P, I, I, P, P, P, P, P],
     },
     "gemm_f32": {
-        "de_gemm_f32": [P, P, P, I, I, I, I, I, I, P],
+        "de_gemm_f32": [P, P, P, I, I, I, I, I, I, P], "de_gemm_f32_small_rows": [],
     },
     "attention_simt": {
         "de_attn_simt_rows_per_tile": [],

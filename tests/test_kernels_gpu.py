@@ -137,8 +137,11 @@ def test_silu_mul(dtype):
 
 
 @pytest.mark.parametrize("n,k,m", [(1, 64, 50), (7, 100, 256), (65, 2051, 331), (130, 176, 64),
-                                   (64, 2048, 2560), (3, 5632, 2048)])
+                                   (64, 2048, 2560), (3, 5632, 2048), (20, 2048, 300),
+                                   (33, 72, 40), (32, 200, 17)])
 def test_gemm_f32(n, k, m):
+    """(up to 32 rows take the kernel of narrow tiles, more the wide one; a row alone and the same
+    row in a batch of more than 32 go through both and must agree bit for bit)"""
     ops = _ops()
     g = torch.Generator().manual_seed(n + k + m)
     x = torch.randn(n, k, generator=g)
