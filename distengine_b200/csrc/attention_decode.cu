@@ -11,11 +11,14 @@
 //     shared memory, so nothing that this launch writes is read from the cache.  The qkv buffer is
 //     left as the product wrote it.
 //   * the merge of a split key range.  The chunks of a range are the blocks of one thread-block
-//     cluster: each leaves its unnormalised result (accumulator, maximum, sum) in its own shared
-//     memory, and after a cluster barrier every block merges a slice of the output from all
-//     blocks' shared memory (distributed shared memory), with no trip through global memory.
+//     cluster.  Every block owns a slice of the output's columns.  When all blocks of the cluster
+//     are through their key tiles (first cluster barrier), every warp stores its unnormalised
+//     result (accumulator, maximum, sum) straight from its registers into the owners' shared
+//     memory (distributed shared memory, in the space the key tiles no longer need); after the
+//     second barrier each owner merges its slice from its own shared memory and writes it out:
+//     no block-level merge first, no remote loads, no trip through global memory.
 //     Ranges longer than a cluster's reach take several clusters; each writes a partial result,
-//     and the cluster that finishes last (a counter per tile and kv head, left at zero again)
+//     and the block that finishes last (a counter per tile and kv head, left at zero again)
 //     merges them in the arithmetic of `de_attn_combine`.  No block spins on another: the cluster
 //     barrier is the hardware's, and every block of a cluster reaches both barriers on every path.
 //   * the cache rows of earlier tokens are requested before the kernel waits for the kernel before
@@ -63,16 +66,30 @@ constexpr int OFF_Q = OFF_V + STAGES * KT * LDS * 2;             // [16][LDS] bf
 constexpr int OFF_KNEW = OFF_Q + ROWS * LDS * 2;                 // [LDS] bf16
 constexpr int OFF_VNEW = OFF_KNEW + LDS * 2;                     // [LDS] bf16
 constexpr int SMEM_TILES = OFF_VNEW + LDS * 2;
-// after the key tiles are done their space is used again:
-constexpr int OFF_RED_O = 0;                                     // [WN][16][D] f32: the warps' results
-constexpr int OFF_RED_M = OFF_RED_O + WN * ROWS * D * 4;         // [WN][16] f32
-constexpr int OFF_RED_L = OFF_RED_M + WN * ROWS * 4;             // [WN][16] f32
-constexpr int OFF_BLK_O = OFF_RED_L + WN * ROWS * 4;             // [16][D] f32: the block's result,
-constexpr int OFF_BLK_M = OFF_BLK_O + ROWS * D * 4;              // [16]         read by the cluster
-constexpr int OFF_BLK_L = OFF_BLK_M + ROWS * 4;                  // [16]
-constexpr int SMEM_MERGE = OFF_BLK_L + ROWS * 4;
-constexpr int SMEM_BYTES = SMEM_TILES > SMEM_MERGE ? SMEM_TILES : SMEM_MERGE;
-static_assert(OFF_BLK_L + ROWS * 4 <= OFF_Q, "the merge area must not reach q (still in use)");
+// After the key tiles are done their space is used again as the place where the cluster's blocks
+// leave their results for this block's slice of the columns:
+//   recv_o  [blocks of the cluster][WN warps][rows][columns of a slice] f32
+//   recv_ml [blocks of the cluster][WN warps][rows][2] f32 (maximum, sum)
+// `rows` = min(16, query heads per kv head); a slice is `cpo` column tiles of 8 (owner of column
+// tile j: j / cpo, cpo = ceil(DT / blocks of the cluster)).
+__host__ __device__ constexpr int slice_tiles(int csize) { return (DT + csize - 1) / csize; }
+__host__ __device__ constexpr int recv_floats(int csize, int rows) {
+    return csize * WN * rows * (slice_tiles(csize) * 8 + 2);
+}
+// shared memory of a launch: the tiles, or the receive area where that is larger (tiny heads)
+static int smem_bytes_for(int rows) {
+    int most = 0;
+    for (int c = 1; c <= MAX_CLUSTER; ++c) most = most > recv_floats(c, rows) ? most : recv_floats(c, rows);
+    const int recv = most * 4;
+    return SMEM_TILES > recv ? SMEM_TILES : recv;
+}
+
+__device__ __forceinline__ void cluster_arrive() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
 
 #ifdef DECODE_TIMING
 // Debugging aid, compiled on request only: wall-clock stamps of one block's phases.
@@ -99,7 +116,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int qkv_stride,
                    float* __restrict__ partial_acc, float* __restrict__ partial_ml,
                    int* __restrict__ counters, const float* __restrict__ inv_freq, int rot,
                    int write_kv, int heads, int kv_heads, int page, float scale, int window,
-                   int* __restrict__ status) {
+                   int recv_rows, int* __restrict__ status) {
     (void)seq_slot;
     (void)seq_pos0;                    // both come with the items
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -111,6 +128,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int qkv_stride,
     __shared__ int s_last;
 
     STAMP(0);
+    DE_TRACE_EVENT(2, 0);
     cg::cluster_group cluster = cg::this_cluster();
     const int csize = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
     const int group = blockIdx.x / csize;                 // (items' cluster, kv head)
@@ -203,6 +221,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int qkv_stride,
 
     STAMP(1);
     pdl_wait();                                       // qkv is the previous kernel's output
+    DE_TRACE_EVENT(2, 1);
     if (!early) {
 #pragma unroll
         for (int t = 0; t < STAGES; ++t) {
@@ -400,125 +419,115 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int qkv_stride,
         l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
     }
 
-    // ---- the block's result: the warps that split the keys, through shared memory
-    float* red_o = reinterpret_cast<float*>(smem_raw + OFF_RED_O);
-    float* red_m = reinterpret_cast<float*>(smem_raw + OFF_RED_M);
-    float* red_l = reinterpret_cast<float*>(smem_raw + OFF_RED_L);
-    float* blk_o = reinterpret_cast<float*>(smem_raw + OFF_BLK_O);
-    float* blk_m = reinterpret_cast<float*>(smem_raw + OFF_BLK_M);
-    float* blk_l = reinterpret_cast<float*>(smem_raw + OFF_BLK_L);
-    __syncthreads();
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        const int r = gid + 8 * i;
-        float* dst = red_o + ((size_t)wn * ROWS + r) * D;
-#pragma unroll
-        for (int j = 0; j < DT; ++j) {
-            dst[j * 8 + 2 * tig] = o_acc[j][2 * i];
-            dst[j * 8 + 2 * tig + 1] = o_acc[j][2 * i + 1];
-        }
-        if (tig == 0) {
-            red_m[wn * ROWS + r] = m_run[i];
-            red_l[wn * ROWS + r] = l_run[i];
-        }
-    }
-    __syncthreads();
-    {
-        // thread (row, column group): the row's factors once, then D / 8 columns
-        static_assert(THREADS == ROWS * 8, "one thread per row and eighth of the columns");
-        const int r = threadIdx.x >> 3, c0 = (threadIdx.x & 7) * (D / 8);
-        float m = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < WN; ++w) m = fmaxf(m, red_m[w * ROWS + r]);
-        float f[WN], l = 0.0f;
-#pragma unroll
-        for (int w = 0; w < WN; ++w) {
-            const float mw = red_m[w * ROWS + r];
-            f[w] = mw == -INFINITY ? 0.0f : fast_exp2((mw - m) * sl);
-            l += red_l[w * ROWS + r] * f[w];
-        }
-#pragma unroll
-        for (int i = 0; i < D / 16; ++i) {
-            float2 acc = make_float2(0.0f, 0.0f);
-#pragma unroll
-            for (int w = 0; w < WN; ++w) {
-                const float2 v = *reinterpret_cast<const float2*>(
-                    red_o + ((size_t)w * ROWS + r) * D + c0 + 2 * i);
-                acc.x = fmaf(v.x, f[w], acc.x);
-                acc.y = fmaf(v.y, f[w], acc.y);
-            }
-            *reinterpret_cast<float2*>(blk_o + r * D + c0 + 2 * i) = acc;
-        }
-        if ((threadIdx.x & 7) == 0) {
-            blk_m[r] = m;                                      // exp2 domain (times sl)
-            blk_l[r] = l;
-        }
-    }
-
-    // ---- the cluster's result: every block merges a slice of (row, pair of features) from all
+    // ---- every block of the cluster is through its tiles: their space is free everywhere
     STAMP(5);
-    cluster.sync();
+    DE_TRACE_EVENT(2, 3);
+    cluster_arrive();
+    cluster_wait();
+    DE_TRACE_EVENT(2, 4);
     STAMP(6);
-    const int total = n_rows * D / 2;                          // pairs
-    const int slice = (total + csize - 1) / csize;
-    const int e_end = min(total, (rank + 1) * slice);
+    const int cpo = slice_tiles(csize);                        // column tiles of a slice
+    const int ld_o = cpo * 8;
+    float* recv_o = reinterpret_cast<float*>(smem_raw);
+    float* recv_ml = recv_o + (size_t)csize * WN * recv_rows * ld_o;
+    // ---- every warp leaves its result with the owners of the columns, from its registers
+    {
+        const int src = rank * WN + wn;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int r = gid + 8 * i;
+            if (r >= n_rows) continue;
+            for (int owner = tig; owner < csize; owner += 4)      // the row's maximum and sum
+                *reinterpret_cast<float2*>(cluster.map_shared_rank(recv_ml, owner) +
+                                           ((size_t)src * recv_rows + r) * 2) =
+                    make_float2(m_run[i], l_run[i]);
+            if (empty) continue;                                   // maximum -inf: nothing to add
+#pragma unroll
+            for (int j = 0; j < DT; ++j) {
+                const int owner = j / cpo, jj = j - owner * cpo;
+                *reinterpret_cast<float2*>(cluster.map_shared_rank(recv_o, owner) +
+                                           ((size_t)src * recv_rows + r) * ld_o + jj * 8 + 2 * tig) =
+                    make_float2(o_acc[j][2 * i], o_acc[j][2 * i + 1]);
+            }
+        }
+    }
+    cluster_arrive();
+    cluster_wait();
+    DE_TRACE_EVENT(2, 5);
+    STAMP(7);
+    // ---- the slice of this block, merged from its own shared memory
     const bool final_here = clusters_per_tile == 1;
     const size_t part_slot = (size_t)it.tile * clusters_per_tile + cluster_in_tile;
     __nv_bfloat16* out_token = out + (size_t)tok * out_stride + (size_t)(hk * g + it.row0) * D;
-    for (int e = rank * slice + threadIdx.x; e < e_end; e += THREADS) {
-        const int r = e / (D / 2), dd = 2 * (e - r * (D / 2));
-        float mc[MAX_CLUSTER], lc[MAX_CLUSTER];
-        float2 ac[MAX_CLUSTER];
-#pragma unroll
-        for (int c = 0; c < MAX_CLUSTER; ++c) {               // independent remote loads
-            mc[c] = -INFINITY; lc[c] = 0.0f; ac[c] = make_float2(0.0f, 0.0f);
-            if (c < csize) {
-                mc[c] = cluster.map_shared_rank(blk_m, c)[r];
-                lc[c] = cluster.map_shared_rank(blk_l, c)[r];
-                ac[c] = *reinterpret_cast<const float2*>(cluster.map_shared_rank(blk_o, c) +
-                                                         r * D + dd);
-            }
-        }
+    const int col0 = rank * ld_o;                               // first column of the slice
+    const int my_cols = max(0, min(D - col0, ld_o));
+    const int sources = csize * WN;
+    // with many sources (clusters of 4 blocks and more) four neighbouring lanes share a pair of
+    // outputs: each merges a quarter of the sources (source p belongs to lane p % 4; there are
+    // 4 x blocks of them), then the four merge theirs; with few, a lane takes all of them
+    static_assert(WN == 4, "a quarter of the sources a lane");
+    const int share = sources >= 16 ? 4 : 1;
+    for (int idx = threadIdx.x; idx < n_rows * (my_cols / 2) * share; idx += THREADS) {
+        const int e = share == 4 ? idx >> 2 : idx, quarter = share == 4 ? idx & 3 : 0;
+        const int r = e / (my_cols / 2), dd = 2 * (e - r * (my_cols / 2));
         float m = -INFINITY;
-#pragma unroll
-        for (int c = 0; c < MAX_CLUSTER; ++c) m = fmaxf(m, mc[c]);
+        for (int p = quarter; p < sources; p += share)
+            m = fmaxf(m, recv_ml[((size_t)p * recv_rows + r) * 2]);
         float l = 0.0f;
         float2 acc = make_float2(0.0f, 0.0f);
+        for (int p = quarter; p < sources; p += share) {
+            const float2 ml = *reinterpret_cast<const float2*>(recv_ml +
+                                                               ((size_t)p * recv_rows + r) * 2);
+            if (ml.x == -INFINITY) continue;                  // no visible key there
+            const float f = fast_exp2((ml.x - m) * sl);
+            const float2 v = *reinterpret_cast<const float2*>(
+                recv_o + ((size_t)p * recv_rows + r) * ld_o + dd);
+            l += ml.y * f;
+            acc.x = fmaf(v.x, f, acc.x);
+            acc.y = fmaf(v.y, f, acc.y);
+        }
+        if (share == 4) {
+            const unsigned group = __activemask();            // (whole groups of four lanes)
+            float m_all = fmaxf(m, __shfl_xor_sync(group, m, 1));
+            m_all = fmaxf(m_all, __shfl_xor_sync(group, m_all, 2));
+            const float mine = m == -INFINITY ? 0.0f : fast_exp2((m - m_all) * sl);
+            l *= mine; acc.x *= mine; acc.y *= mine;
 #pragma unroll
-        for (int c = 0; c < MAX_CLUSTER; ++c) {
-            if (mc[c] == -INFINITY) continue;                 // no visible key there (or no block)
-            const float f = fast_exp2((mc[c] - m) * sl);
-            l += lc[c] * f;
-            acc.x = fmaf(ac[c].x, f, acc.x);
-            acc.y = fmaf(ac[c].y, f, acc.y);
+            for (int o = 1; o < 4; o <<= 1) {
+                l += __shfl_xor_sync(group, l, o);
+                acc.x += __shfl_xor_sync(group, acc.x, o);
+                acc.y += __shfl_xor_sync(group, acc.y, o);
+            }
+            m = m_all;
+            if (quarter != 0) continue;
         }
         if (final_here) {
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-            *reinterpret_cast<unsigned*>(out_token + r * D + dd) = pack_bf16(acc.x * inv, acc.y * inv);
+            *reinterpret_cast<unsigned*>(out_token + r * D + col0 + dd) =
+                pack_bf16(acc.x * inv, acc.y * inv);
         } else {
-            const size_t idx = (part_slot * kv_heads + hk) * ROWS + r;
-            *reinterpret_cast<float2*>(partial_acc + idx * D + dd) = acc;
-            if (dd == 0) {
-                partial_ml[idx * 2] = m * scale;              // natural-log domain, as merged
-                partial_ml[idx * 2 + 1] = l;
+            const size_t idx_p = (part_slot * kv_heads + hk) * ROWS + r;
+            *reinterpret_cast<float2*>(partial_acc + idx_p * D + col0 + dd) = acc;
+            if (col0 + dd == 0) {
+                partial_ml[idx_p * 2] = m * scale;            // natural-log domain, as merged
+                partial_ml[idx_p * 2 + 1] = l;
             }
         }
     }
-    if (!final_here) __threadfence();
-    STAMP(7);
-    cluster.sync();                    // nobody leaves while its shared memory may still be read
     STAMP(8);
-    if (final_here || rank != 0) return;
+    DE_TRACE_EVENT(2, 2);
+    if (final_here) return;
 
-    // ---- several clusters a tile: the one that finishes last merges their partial results, in
+    // ---- several clusters a tile: the block that finishes last merges their partial results, in
     // ascending order of the chunks.  Clusters of padding only do not count and are not counted on.
     const int live_clusters = (it.chunks + csize - 1) / csize;
     if (cluster_in_tile >= live_clusters) return;
+    __threadfence();                                   // this block's slice of the partial result
+    __syncthreads();
     if (threadIdx.x == 0) {
-        __threadfence();
         int* counter = counters + (size_t)it.tile * kv_heads + hk;
         const int before = atomicAdd(counter, 1);
-        s_last = before == live_clusters - 1;
+        s_last = before == live_clusters * csize - 1;
         if (s_last) *counter = 0;                    // as the next launch expects it
     }
     __syncthreads();
@@ -574,20 +583,18 @@ DE_EXPORT int de_attn_decode_stamps(unsigned long long* host_out) {
 DE_EXPORT int de_attn_decode_head_dim() { return D; }
 DE_EXPORT int de_attn_decode_max_cluster() { return MAX_CLUSTER; }
 // Blocks of the kernel that an SM holds at once (registers and shared memory), or 0 if unknown.
-DE_EXPORT int de_attn_decode_blocks_per_sm() {
-    static int blocks = -1;
-    if (blocks < 0) {
-        if (SMEM_BYTES > 48 * 1024 &&
-            cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 SMEM_BYTES) != cudaSuccess)
-            return 0;
-        int n = 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attn_decode_kernel, THREADS,
-                                                          SMEM_BYTES) != cudaSuccess)
-            return 0;
-        blocks = n;
-    }
-    return blocks;
+// (`group`: query heads per kv head; the receive area of the merge grows with it for tiny heads)
+DE_EXPORT int de_attn_decode_blocks_per_sm(int group) {
+    const int smem = smem_bytes_for(group < ROWS ? group : ROWS);
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             smem) != cudaSuccess)
+        return 0;
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attn_decode_kernel, THREADS, smem) !=
+        cudaSuccess)
+        return 0;
+    return n;
 }
 
 // `items`: tiles x `cap` work items (see the head of the file), `cluster` blocks a cluster (1 to 8;
@@ -614,6 +621,8 @@ DE_EXPORT int de_attn_decode(const void* qkv, int qkv_stride, void* out, int out
     if (qkv_stride % 8 != 0 || out_stride % 2 != 0 || ((uintptr_t)qkv & 15) ||
         ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15))
         return -3;
+    const int recv_rows = heads / kv_heads < ROWS ? heads / kv_heads : ROWS;
+    const int SMEM_BYTES = smem_bytes_for(recv_rows);
     if (SMEM_BYTES > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
@@ -655,5 +664,6 @@ DE_EXPORT int de_attn_decode(const void* qkv, int qkv_stride, void* out, int out
         &cfg, attn_decode_kernel, (const __nv_bfloat16*)qkv, qkv_stride, (__nv_bfloat16*)out,
         out_stride, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, block_table, table_stride,
         num_pages, seq_slot, seq_qstart, seq_pos0, (const WorkItem*)items, cap, partial_acc,
-        partial_ml, counters, inv_freq, rot, write_kv, heads, kv_heads, page, scale, window, status));
+        partial_ml, counters, inv_freq, rot, write_kv, heads, kv_heads, page, scale, window,
+        recv_rows, status));
 }

@@ -134,7 +134,50 @@ static inline int de_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, siz
     return de_check(cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...));
 }
 
+// ---------------------------------------------------------------------------------------------
+// A timeline for measurements, compiled on request only (-DDE_TRACE): thread 0 of a block appends
+// (tag, block, SM, event, nanoseconds of the global timer) to a buffer of the library, which
+// de_trace_dump copies to the host and empties.  Events: 0 block entered, 1 its wait for the
+// kernel before it returned, 2 block done; kernels may add their own.  Without DE_TRACE the macro
+// is empty and nothing of this exists.
+// ---------------------------------------------------------------------------------------------
+#ifdef DE_TRACE
+constexpr unsigned DE_TRACE_CAP = 1u << 16;
+__device__ unsigned long long de_trace_buf[DE_TRACE_CAP * 2];
+__device__ unsigned de_trace_count;
+__device__ __forceinline__ void de_trace_event(unsigned tag, unsigned event) {
+    if (threadIdx.x != 0) return;
+    unsigned long long t;
+    unsigned sm;
+    asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
+    asm volatile("mov.u32 %0, %%smid;\n" : "=r"(sm));
+    const unsigned at = atomicAdd(&de_trace_count, 1u);
+    if (at >= DE_TRACE_CAP) return;
+    de_trace_buf[2 * at] = ((unsigned long long)tag << 48) | ((unsigned long long)event << 40) |
+                           ((unsigned long long)sm << 24) | (unsigned long long)(blockIdx.x & 0xffffff);
+    de_trace_buf[2 * at + 1] = t;
+}
+#define DE_TRACE_EVENT(tag, event) de_trace_event(tag, event)
+#define DE_DEFINE_TRACE_DUMP                                                                    \
+    DE_EXPORT int de_trace_dump(unsigned long long* host_out, int max_events) {                 \
+        unsigned count = 0;                                                                     \
+        cudaError_t e = cudaMemcpyFromSymbol(&count, de_trace_count, sizeof(count));            \
+        if (e != cudaSuccess) return -(int)e;                                                   \
+        if (count > DE_TRACE_CAP) count = DE_TRACE_CAP;                                         \
+        if ((int)count > max_events) count = (unsigned)max_events;                              \
+        e = cudaMemcpyFromSymbol(host_out, de_trace_buf, (size_t)count * 16);                   \
+        if (e != cudaSuccess) return -(int)e;                                                   \
+        const unsigned zero = 0;                                                                \
+        cudaMemcpyToSymbol(de_trace_count, &zero, sizeof(zero));                                \
+        return (int)count;                                                                      \
+    }
+#else
+#define DE_TRACE_EVENT(tag, event) do { } while (0)
+#define DE_DEFINE_TRACE_DUMP
+#endif
+
 #define DE_DEFINE_PDL_SWITCH                                               \
+    DE_DEFINE_TRACE_DUMP                                                   \
     DE_EXPORT int de_set_pdl(int on) { g_pdl = on ? 1 : 0; return 0; }     \
     DE_EXPORT int de_set_carveout(int percent) {                           \
         g_carveout = percent < 0 ? -1 : (percent > 100 ? 100 : percent);   \

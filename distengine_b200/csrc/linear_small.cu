@@ -108,6 +108,7 @@ linear_small_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfl
     __shared__ float red[WARPS][SETS][16][NT * 8 + 1];
     __shared__ float row_factor[NT * 8];
 
+    DE_TRACE_EVENT(1, 0);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * ROWS;
@@ -202,6 +203,7 @@ linear_small_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfl
     // after the main loop.
     pdl_trigger();
     pdl_wait();                                   // x is the previous kernel's output
+    DE_TRACE_EVENT(1, 1);
 
     // requested now, used in the epilogue: this thread's element of the residual, and the shares
     // of the rows' sums of squares (warp w adds up rows w and w + 8, its lanes every 32nd share)
@@ -325,6 +327,7 @@ linear_small_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfl
         }
         if (live) out[(size_t)m * ldo + n] = to_out<OutT>(y);
     }
+    DE_TRACE_EVENT(1, 2);
 }
 
 template <int NT, int ROWS, bool GATED, bool NORM, typename OutT>
@@ -347,7 +350,10 @@ int launch(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, i
 }
 
 // few weight rows: blocks of 8 rows, so that there are blocks for every SM
-bool few_rows(int n_out) { return n_out < 16 * 2 * 148; }
+#ifndef FEW_ROWS_LIMIT
+#define FEW_ROWS_LIMIT (16 * 2 * 148)
+#endif
+bool few_rows(int n_out) { return n_out < FEW_ROWS_LIMIT; }
 
 template <bool GATED, bool NORM, typename OutT>
 int pick(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int m_rows,

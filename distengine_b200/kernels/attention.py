@@ -137,7 +137,7 @@ class AttentionLauncher:
             span = min(span, self.window)
         if self._decode_blocks_per_sm is None:
             lib = library.load(*self.decode_module)
-            self._decode_blocks_per_sm = min(int(lib.de_attn_decode_blocks_per_sm()) or 4, 4)
+            self._decode_blocks_per_sm = min(int(lib.de_attn_decode_blocks_per_sm(self.group)) or 4, 4)
         cluster, clusters, chunk = force_split or choose_decode_split(
             tiles, self.kv_heads, span, int(os.environ.get("DISTENGINE_B200_DECODE_CLUSTER", "8")),
             self._decode_blocks_per_sm, sm_count=self.sm_count())

@@ -63,7 +63,7 @@ SIGNATURES: dict[str, dict[str, list]] = {
     },
     "attention_decode": {
         "de_attn_decode_head_dim": [], "de_attn_decode_max_cluster": [],
-        "de_attn_decode_blocks_per_sm": [],
+        "de_attn_decode_blocks_per_sm": [I],
         "de_attn_decode": [P, I, P, I, P, P, P, I, I, P, P, P, P, I, I, I, P, P, P, P, I, I, I, I,
                            I, I, F, I, P, P],
     },
