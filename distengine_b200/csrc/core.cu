@@ -281,9 +281,12 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride,
 }
 
 // The same for bfloat16 rows of 16-byte pieces with every feature rotated (rot == d, d a multiple
-// of 16): a thread takes 8 pairs of one head - the pieces j .. j + 7 of both halves - or one piece
-// of a value row, and requests all it needs at once; one pass instead of a loop over heads whose
-// loads wait for the stores before them.
+// of 16).  A block takes a token: its first threads form the cosines and sines of the token's
+// d / 2 angles once, in shared memory, for all heads (that is what the kernel's time went into when
+// every thread formed its own: 36 heads repeat the same angles); then a thread takes 8 pairs of one
+// head - the pieces j .. j + 7 of both halves - or one piece of a value row, and requests all it
+// needs at once.
+constexpr int ROPE_MAX_HALF = 128;                           // head sizes up to 256
 __global__ void rope_kv_write_bf16x8_kernel(__nv_bfloat16* __restrict__ qkv, int row_stride,
                                             const int* __restrict__ positions,
                                             const int* __restrict__ token_slot,
@@ -293,77 +296,76 @@ __global__ void rope_kv_write_bf16x8_kernel(__nv_bfloat16* __restrict__ qkv, int
                                             const int* __restrict__ block_table, int table_stride,
                                             int page, int write_kv, int num_pages, int n_tokens,
                                             int* __restrict__ status) {
+    __shared__ float cos_s[ROPE_MAX_HALF], sin_s[ROPE_MAX_HALF];
+    __shared__ int page_s;
     const int half = d / 2;
     const int per_head = half / 8;                           // rotation items of a head
     const int rotations = (heads + kv_heads) * per_head;
     const int per_token = rotations + kv_heads * (d / 8);    // then the pieces of the value rows
-    const long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    const bool live = item < (long long)n_tokens * per_token;
-    const int n = live ? (int)(item / per_token) : 0;
-    const int local = live ? (int)(item - (long long)n * per_token) : 0;
+    const int n = blockIdx.x;
     const int pos = positions[n];
-    const bool rotation = local < rotations;
-    const int h = rotation ? local / per_head : (local - rotations) / (d / 8);
-    const int piece = rotation ? local - h * per_head : (local - rotations) - h * (d / 8);
-    // the angles do not depend on the kernel before this one
-    float c[8], sn[8];
-    if (rotation && inv_freq != nullptr) {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            const float angle = (float)pos * inv_freq[piece * 8 + e];
-            c[e] = cosf(angle);
-            sn[e] = sinf(angle);
-        }
-    } else {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) { c[e] = 1.0f; sn[e] = 0.0f; }
+    // the angles and the page do not depend on the kernel before this one
+    for (int j = threadIdx.x; j < half; j += blockDim.x) {
+        const float angle = inv_freq != nullptr ? (float)pos * inv_freq[j] : 0.0f;
+        cos_s[j] = cosf(angle);
+        sin_s[j] = sinf(angle);
     }
-    const bool to_cache = live && write_kv != 0 && (!rotation || h >= heads);
-    size_t kv_offset = 0;
-    bool can_write = to_cache;
-    if (to_cache) {
-        const int page_id = block_table[(size_t)token_slot[n] * table_stride + pos / page];
-        if (page_id < 0 || page_id >= num_pages) {      // a table without a page here: record, skip
-            atomicExch(status, 1);
-            can_write = false;
+    if (threadIdx.x == blockDim.x - 1) {
+        int page_id = -1;
+        if (write_kv != 0) {
+            page_id = block_table[(size_t)token_slot[n] * table_stride + pos / page];
+            if (page_id < 0 || page_id >= num_pages) {  // a table without a page here: record, skip
+                atomicExch(status, 1);
+                page_id = -1;
+            }
         }
-        const int kv_head = rotation ? h - heads : h;
-        kv_offset = (((size_t)page_id * kv_heads + kv_head) * page + (size_t)(pos % page)) * d;
+        page_s = page_id;
     }
     pdl_wait();
     pdl_trigger();
-    if (!live) return;
+    __syncthreads();
+    const int page_id = page_s;
     __nv_bfloat16* row = qkv + (size_t)n * row_stride;
-    if (!rotation) {
-        if (can_write)
-            *reinterpret_cast<uint4*>(v_pages + kv_offset + piece * 8) =
-                *reinterpret_cast<const uint4*>(row + (size_t)(heads + kv_heads + h) * d + piece * 8);
-        return;
-    }
-    __nv_bfloat16* x = row + (size_t)h * d + piece * 8;
-    uint4 lo = *reinterpret_cast<const uint4*>(x), hi = *reinterpret_cast<const uint4*>(x + half);
-    unsigned* lo_words[4] = {&lo.x, &lo.y, &lo.z, &lo.w};
-    unsigned* hi_words[4] = {&hi.x, &hi.y, &hi.z, &hi.w};
+    for (int local = threadIdx.x; local < per_token; local += blockDim.x) {
+        const bool rotation = local < rotations;
+        const int h = rotation ? local / per_head : (local - rotations) / (d / 8);
+        const int piece = rotation ? local - h * per_head : (local - rotations) - h * (d / 8);
+        const int kv_head = rotation ? h - heads : h;
+        const size_t kv_offset =
+            (((size_t)(page_id < 0 ? 0 : page_id) * kv_heads + (kv_head < 0 ? 0 : kv_head)) * page +
+             (size_t)(pos % page)) * d;
+        if (!rotation) {
+            if (page_id >= 0)
+                *reinterpret_cast<uint4*>(v_pages + kv_offset + piece * 8) =
+                    *reinterpret_cast<const uint4*>(row + (size_t)(heads + kv_heads + h) * d +
+                                                    piece * 8);
+            continue;
+        }
+        __nv_bfloat16* x = row + (size_t)h * d + piece * 8;
+        uint4 lo = *reinterpret_cast<const uint4*>(x), hi = *reinterpret_cast<const uint4*>(x + half);
+        unsigned* lo_words[4] = {&lo.x, &lo.y, &lo.z, &lo.w};
+        unsigned* hi_words[4] = {&hi.x, &hi.y, &hi.z, &hi.w};
 #pragma unroll
-    for (int e = 0; e < 8; e += 2) {                 // two elements a 32-bit word
-        const float a0 = __uint_as_float(*lo_words[e / 2] << 16);
-        const float a1 = __uint_as_float(*lo_words[e / 2] & 0xffff0000u);
-        const float b0 = __uint_as_float(*hi_words[e / 2] << 16);
-        const float b1 = __uint_as_float(*hi_words[e / 2] & 0xffff0000u);
-        float fa0, fb0, fa1, fb1;
-        rope_rotate(a0, b0, c[e], sn[e], fa0, fb0);
-        rope_rotate(a1, b1, c[e + 1], sn[e + 1], fa1, fb1);
-        const __nv_bfloat162 ra = __floats2bfloat162_rn(fa0, fa1);
-        const __nv_bfloat162 rb = __floats2bfloat162_rn(fb0, fb1);
-        *lo_words[e / 2] = *reinterpret_cast<const unsigned*>(&ra);
-        *hi_words[e / 2] = *reinterpret_cast<const unsigned*>(&rb);
-    }
-    if (h < heads) {
-        *reinterpret_cast<uint4*>(x) = lo;
-        *reinterpret_cast<uint4*>(x + half) = hi;
-    } else if (can_write) {
-        *reinterpret_cast<uint4*>(k_pages + kv_offset + piece * 8) = lo;
-        *reinterpret_cast<uint4*>(k_pages + kv_offset + half + piece * 8) = hi;
+        for (int e = 0; e < 8; e += 2) {                 // two elements a 32-bit word
+            const float a0 = __uint_as_float(*lo_words[e / 2] << 16);
+            const float a1 = __uint_as_float(*lo_words[e / 2] & 0xffff0000u);
+            const float b0 = __uint_as_float(*hi_words[e / 2] << 16);
+            const float b1 = __uint_as_float(*hi_words[e / 2] & 0xffff0000u);
+            float fa0, fb0, fa1, fb1;
+            rope_rotate(a0, b0, cos_s[piece * 8 + e], sin_s[piece * 8 + e], fa0, fb0);
+            rope_rotate(a1, b1, cos_s[piece * 8 + e + 1], sin_s[piece * 8 + e + 1], fa1, fb1);
+            const __nv_bfloat162 ra = __floats2bfloat162_rn(fa0, fa1);
+            const __nv_bfloat162 rb = __floats2bfloat162_rn(fb0, fb1);
+            *lo_words[e / 2] = *reinterpret_cast<const unsigned*>(&ra);
+            *hi_words[e / 2] = *reinterpret_cast<const unsigned*>(&rb);
+        }
+        if (h < heads) {
+            *reinterpret_cast<uint4*>(x) = lo;
+            *reinterpret_cast<uint4*>(x + half) = hi;
+        } else if (page_id >= 0) {
+            *reinterpret_cast<uint4*>(k_pages + kv_offset + piece * 8) = lo;
+            *reinterpret_cast<uint4*>(k_pages + kv_offset + half + piece * 8) = hi;
+        }
     }
 }
 
@@ -375,11 +377,12 @@ DE_EXPORT int de_rope_kv_write(int dtype, void* qkv, int row_stride, const int* 
     if (n <= 0) return 0;
     if (rot < 0 || rot > d || (rot & 1)) return -2;
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == DE_BF16 && d % 16 == 0 && (inv_freq == nullptr || rot == d) && row_stride % 8 == 0 &&
+    if (dtype == DE_BF16 && d % 16 == 0 && d <= 2 * ROPE_MAX_HALF && (inv_freq == nullptr || rot == d) &&
+        row_stride % 8 == 0 &&
         ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)k_pages & 15) == 0 && ((uintptr_t)v_pages & 15) == 0) {
-        const long long items = (long long)n * ((heads + kv_heads) * (d / 16) + kv_heads * (d / 8));
-        return de_launch(rope_kv_write_bf16x8_kernel, dim3((unsigned)((items + 255) / 256)), dim3(256),
-                         0, s, (__nv_bfloat16*)qkv, row_stride, positions, token_slot, inv_freq,
+        const int per_token = (heads + kv_heads) * (d / 16) + kv_heads * (d / 8);
+        const int threads = per_token >= 256 ? 256 : (per_token + 31) / 32 * 32;
+        return de_launch(rope_kv_write_bf16x8_kernel, dim3((unsigned)n), dim3(threads), 0, s, (__nv_bfloat16*)qkv, row_stride, positions, token_slot, inv_freq,
                          heads, kv_heads, d, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages,
                          block_table, table_stride, page, write_kv, num_pages, n, status);
     }
