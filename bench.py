@@ -452,6 +452,81 @@ def workload_mixed(args, warmup: int, steps: int) -> int:
     return 0
 
 
+def timeline(args) -> int:
+    """Prints when the blocks of every kernel of one decode step entered, passed their wait for
+    the kernel before them and finished (first / median / last block, microseconds from the
+    step's first event), from stamps inside the kernels.  The kernels carry the stamps only when
+    they are built with DISTENGINE_B200_DEFINES=DE_TRACE; the step runs as it does in the
+    benchmark (a replayed CUDA graph)."""
+    import collections
+    import ctypes
+    import numpy as np
+    import torch
+    from distengine_b200 import Engine, EngineConfig
+    from distengine_b200.engine.step import StepEntry
+    from distengine_b200.kernels import library, ops
+    if "DE_TRACE" not in os.environ.get("DISTENGINE_B200_DEFINES", ""):
+        print("bench.py --timeline needs DISTENGINE_B200_DEFINES=DE_TRACE in the environment")
+        return 2
+    folder = model_folder(args.layers)
+    engine = Engine(folder, EngineConfig(dtype="bfloat16", block_size=PAGE,
+                                         num_blocks=64 * (PROMPT + 64) // PAGE,
+                                         decode_batch_size=64, max_batch_tokens=PREFILL,
+                                         use_graphs=not args.no_graphs))
+    runner, rng, vocab = engine.runner, np.random.default_rng(0), MODEL["vocab_size"]
+    ids = [f"t{i}" for i in range(args.batch)]
+    for rid in ids:
+        runner.step([StepEntry(rid, [int(t) for t in rng.integers(0, vocab, size=PROMPT)], [])])
+
+    def step():
+        entries = [StepEntry(r, [int(rng.integers(0, vocab))], [0]) for r in ids]
+        ops.sample_rows(runner.step(entries), engine.sampler.ids[: args.batch])
+
+    for _ in range(6):
+        step()
+    torch.cuda.synchronize()
+    buffer = (ctypes.c_ulonglong * (2 << 16))()
+
+    def dump(lib):
+        if not hasattr(lib, "de_trace_dump"):
+            return np.zeros((0, 2), dtype=np.uint64)
+        lib.de_trace_dump.argtypes = [ctypes.c_void_p, ctypes.c_int]
+        lib.de_trace_dump.restype = ctypes.c_int
+        count = lib.de_trace_dump(buffer, 1 << 16)
+        return np.frombuffer(buffer, dtype=np.uint64, count=2 * max(count, 0)).reshape(-1, 2).copy()
+
+    libs = dict(library._loaded)
+    for lib in libs.values():
+        dump(lib)                                        # empties the buffers
+    step()
+    torch.cuda.synchronize()
+    events = []
+    for (module, _), lib in libs.items():
+        for word, when in dump(lib):
+            word = int(word)
+            events.append((int(when), module, word >> 48, (word >> 40) & 0xff, word & 0xffffff))
+    if not events:
+        print("no events: were the kernels built with DE_TRACE?")
+        return 2
+    events.sort()
+    start = events[0][0]
+    per = collections.defaultdict(lambda: collections.defaultdict(list))
+    seen = collections.Counter()
+    for when, module, tag, event, block in events:
+        if event == 0:
+            seen[(module, tag, block)] += 1
+        per[(module, tag, seen[(module, tag, block)])][event].append((when - start) / 1e3)
+    print("us from the step's first event; event: first / median / last (blocks); events: 0 block "
+          "entered, 1 its wait for the kernel before it is over, 2 block done, 3-5 kernel's own")
+    for key, by_event in sorted(per.items(), key=lambda kv: min(kv[1].get(0, [1e9]))):
+        if 0 not in by_event:
+            continue
+        text = " ".join(f"e{e}:{min(v):7.2f}/{statistics.median(v):7.2f}/{max(v):7.2f}({len(v)})"
+                        for e, v in sorted(by_event.items()))
+        print(f"{key[0]:17s} tag {key[1]:5d} launch {key[2]:3d}  {text}")
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -464,6 +539,9 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=MODEL["num_hidden_layers"],
                         help="fewer layers than the configuration's 22, for small profiling runs")
     parser.add_argument("--no-graphs", action="store_true")
+    parser.add_argument("--timeline", action="store_true",
+                        help="print one decode step's in-kernel timeline (kernels built with "
+                             "DISTENGINE_B200_DEFINES=DE_TRACE)")
     parser.add_argument("--workload", default="headline",
                         choices=["headline", "mixed", "long", "fp32"])
     args = parser.parse_args()
@@ -476,6 +554,8 @@ def main() -> int:
     warmup, steps = max(args.warmup, 3), max(args.steps, 1)
     if args.impl == "reference":
         return reference_arm(args, warmup, steps)
+    if args.timeline:
+        return timeline(args)
     if args.workload != "headline":
         return {"mixed": workload_mixed, "long": workload_long,
                 "fp32": workload_fp32}[args.workload](args, warmup, steps)

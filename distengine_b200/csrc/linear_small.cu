@@ -108,7 +108,7 @@ linear_small_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfl
     __shared__ float red[WARPS][SETS][16][NT * 8 + 1];
     __shared__ float row_factor[NT * 8];
 
-    DE_TRACE_EVENT(1, 0);
+    DE_TRACE_EVENT(n_out, 0);           // (the tag tells the products of a layer apart)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * ROWS;
@@ -203,7 +203,7 @@ linear_small_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfl
     // after the main loop.
     pdl_trigger();
     pdl_wait();                                   // x is the previous kernel's output
-    DE_TRACE_EVENT(1, 1);
+    DE_TRACE_EVENT(n_out, 1);           // (the tag tells the products of a layer apart)
 
     // requested now, used in the epilogue: this thread's element of the residual, and the shares
     // of the rows' sums of squares (warp w adds up rows w and w + 8, its lanes every 32nd share)
@@ -327,7 +327,7 @@ linear_small_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfl
         }
         if (live) out[(size_t)m * ldo + n] = to_out<OutT>(y);
     }
-    DE_TRACE_EVENT(1, 2);
+    DE_TRACE_EVENT(n_out, 2);           // (the tag tells the products of a layer apart)
 }
 
 template <int NT, int ROWS, bool GATED, bool NORM, typename OutT>
