@@ -179,7 +179,10 @@ def test_toy_architecture_is_built_and_stepped(dtype_name, model_root):
     requests = {f"t{i}": [int(t) for t in rng.integers(0, 97, size=n)]
                 for i, n in enumerate([50, 9, 77, 30, 64])}
     want = {rid: _plain_toy(config, weights, ids, dtype).numpy() for rid, ids in requests.items()}
+    # (the last 32 tokens one by one: steps of single tokens, where the run that reads another
+    # run's cache goes through the one-launch decode attention)
     for steps, max_tokens in ((th.schedule_whole(requests), 128),
+                              (th.schedule_tail(requests, 32), 128),
                               (th.schedule_portions(requests), 128),
                               (th.schedule_mixed(requests, 256, seed=1), 256)):
         runner = build_runner(folder, dtype_name, max_tokens, page_size=16,
