@@ -536,14 +536,17 @@ attn_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
 #pragma unroll
                 for (int i = 0; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(sv[c][i]));
             const float m_tile = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-            // p of the previous tile has been multiplied: its buffer is free, and o is at rest
             if (tid == 0) STAMP(0, tile, 2);
-            if (tile > 0 && ok) ok = mbar_wait(&o_done[x], (tile - 1) & 1, status);
-            if (tid == 0) STAMP(0, tile, 3);
-            // ---- raise the reference where the maximum has run away from it
+            // ---- raise the reference where the maximum has run away from it.  That rescales o,
+            // which must be at rest: the previous tile's product is waited for first.  Otherwise
+            // (nearly always) the exponentials below are formed before that wait: only p's
+            // buffer needs the product to be over, not the arithmetic.
             const bool raise = m_tile > m_ref && (m_ref == -INFINITY ||
                                                   (m_tile - m_ref) * sl > RESCALE_AFTER);
+            bool o_at_rest = tile == 0;
             if (tile > 0 && __any_sync(0xffffffffu, raise && m_ref != -INFINITY)) {
+                if (ok) ok = mbar_wait(&o_done[x], (tile - 1) & 1, status);
+                o_at_rest = true;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 const float f = (raise && m_ref != -INFINITY) ? fast_exp2((m_ref - m_tile) * sl) : 1.0f;
 #pragma unroll 1
@@ -563,6 +566,7 @@ attn_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
             // sub-tile (key / 64), 16-byte chunk ((key % 64) / 8) xor (rowi % 8)
             const float m_off = m_ref == -INFINITY ? 0.0f : -m_ref * sl;
             float l4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            uint4 pu[16];                        // the row of p, packed (in place of the scores)
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
 #pragma unroll
@@ -576,12 +580,21 @@ attn_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
                     uint4 u;
                     u.x = pack2(p[0], p[1]); u.y = pack2(p[2], p[3]);
                     u.z = pack2(p[4], p[5]); u.w = pack2(p[6], p[7]);
-                    const int chunk = ((32 * c + i) & 63) >> 3;
-                    *reinterpret_cast<uint4*>(p_row + (c >> 1) * TILE_BYTES +
-                                              ((chunk ^ (rowi & 7)) << 4)) = u;
+                    pu[c * 4 + i / 8] = u;
                 }
             }
             l_run += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+            // p of the previous tile has been multiplied: its buffer is free
+            if (!o_at_rest && ok) ok = mbar_wait(&o_done[x], (tile - 1) & 1, status);
+            if (tid == 0) STAMP(0, tile, 3);
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+                for (int i = 0; i < 32; i += 8) {
+                    const int chunk = ((32 * c + i) & 63) >> 3;
+                    *reinterpret_cast<uint4*>(p_row + (c >> 1) * TILE_BYTES +
+                                              ((chunk ^ (rowi & 7)) << 4)) = pu[c * 4 + i / 8];
+                }
             if (tid == 0) STAMP(0, tile, 4);
             // Pages come whole: rows of v beyond the range (the rest of the last page, or keys
             // before a window) may hold anything, and 0 * NaN is NaN in the product.  Row rowi of
