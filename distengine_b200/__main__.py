@@ -9,6 +9,12 @@ from ``--weights-seed``), ``--prompt-ids`` gives token ids directly, and ``--pro
 ``tokenizer.json`` in the model folder.
 ``--decode-batch-size`` is the reference's benchmark flag (src/utils/benchmark.py:593).
 ``random-model`` writes a model folder from a configuration and a seed.
+``bench`` runs a set of requests with arrival times through the engine and reports what the
+reference's benchmark reports of its requests (src/utils/benchmark.py:585-609: ``--repeats``,
+``--output``, a folder that must not exist yet and receives ``baseline.json``, and
+``--decode-batch-size``); its default request set is the reference's smoke workload
+(src/utils/benchmark.py:26-40: six requests with prompts of 1, 8 and 16 tokens, four new tokens
+each, Poisson arrivals at 100 requests a second from seed 42).
 """
 
 from __future__ import annotations
@@ -30,7 +36,9 @@ def _tokenizer(model_dir: str):
     return Tokenizer.from_file(path)
 
 
-def _generate(args: argparse.Namespace) -> int:
+def _with_model_folder(args: argparse.Namespace, run) -> int:
+    """``run(args)`` with ``args.model`` naming a model folder: the given one, or a temporary one
+    with random weights for ``--random CONFIG``."""
     if args.max_new_tokens <= 0:
         raise SystemExit("--max-new-tokens must be positive")
     if (args.model is None) == (args.random is None):
@@ -45,10 +53,65 @@ def _generate(args: argparse.Namespace) -> int:
         args.model = write_random_model(config_json, os.path.join(scratch.name, "model"),
                                         args.weights_seed, dtype=args.dtype)
     try:
-        return _generate_from_folder(args)
+        return run(args)
     finally:
         if scratch is not None:
             scratch.cleanup()
+
+
+def _generate(args: argparse.Namespace) -> int:
+    return _with_model_folder(args, _generate_from_folder)
+
+
+def _bench(args: argparse.Namespace) -> int:
+    if args.repeats <= 0:
+        raise SystemExit("--repeats must be positive")
+    if os.path.exists(args.output):
+        raise SystemExit("Choose a new output directory")
+    return _with_model_folder(args, _bench_from_folder)
+
+
+def _bench_from_folder(args: argparse.Namespace) -> int:
+    from .config.engine import EngineConfig
+    from .engine import benchmark
+    from .engine.engine import Engine
+
+    lengths = [int(t) for t in args.prompt_lengths.replace(",", " ").split()]
+    config = EngineConfig(dtype=args.dtype, block_size=args.block_size,
+                          num_blocks=args.num_blocks, decode_batch_size=args.decode_batch_size,
+                          max_batch_tokens=args.max_batch_tokens, device=args.device)
+    engine = Engine(args.model, config)
+    workload = benchmark.make_workload(args.num_requests, lengths, args.max_new_tokens,
+                                       engine.model.config.vocabulary, args.seed, args.rate_rps)
+    # once unmeasured: kernels are compiled and loaded, buffers sized, decode steps captured
+    benchmark.run_workload(engine, [benchmark.BenchRequest(f"warm-{r.request_id}", 0.0,
+                                                           r.prompt_token_ids, r.max_new_tokens)
+                                    for r in workload])
+    runs = []
+    for repeat in range(args.repeats):
+        named = [benchmark.BenchRequest(f"run{repeat}-{r.request_id}", r.arrival_s,
+                                        r.prompt_token_ids, r.max_new_tokens) for r in workload]
+        runs.append(benchmark.run_workload(engine, named))
+    report = {
+        "workload": {"num_requests": args.num_requests, "prompt_lengths": lengths,
+                     "max_new_tokens": args.max_new_tokens, "rate_rps": args.rate_rps,
+                     "seed": args.seed, "arrival_mode": "poisson" if args.rate_rps > 0 else "burst"},
+        "engine": {"model": os.path.abspath(args.model), "dtype": args.dtype,
+                   "decode_batch_size": args.decode_batch_size,
+                   "max_batch_tokens": args.max_batch_tokens, "block_size": args.block_size},
+        "runs": runs,
+    }
+    report.update(benchmark.aggregate(runs))
+    os.makedirs(args.output)
+    path = os.path.join(args.output, "baseline.json")
+    with open(path, "w") as handle:
+        json.dump(report, handle, indent=2)
+    rates = report["aggregate"]
+    print(f"requests/s {rates['request_throughput_rps']['mean']:.2f}  output tokens/s "
+          f"{rates['completed_output_tokens_per_s']['mean']:.1f}  "
+          f"ttft p50 {report['latency_across_runs']['ttft_s']['p50']['mean'] * 1e3:.2f} ms")
+    print(f"Saved {path}")
+    return 0
 
 
 def _generate_from_folder(args: argparse.Namespace) -> int:
@@ -133,6 +196,30 @@ def main(argv: "list[str] | None" = None) -> int:
     rnd.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     rnd.add_argument("--norm-init", default="ones", choices=["ones", "uniform"])
     rnd.set_defaults(run=_random_model)
+
+    ben = sub.add_parser("bench", help="run a request set through the engine; request "
+                                       "throughput, output tokens a second, latencies")
+    ben.add_argument("--model", help="folder with config.json, model.safetensors")
+    ben.add_argument("--random", metavar="CONFIG", help="a config.json: random weights in a "
+                     "temporary model folder")
+    ben.add_argument("--weights-seed", type=int, default=0, help="seed of --random's weights")
+    ben.add_argument("--repeats", type=int, default=3)
+    ben.add_argument("--output", required=True, help="a new folder; receives baseline.json")
+    ben.add_argument("--decode-batch-size", type=int, default=64,
+                     help="most requests decoded together in one step")
+    ben.add_argument("--num-requests", type=int, default=6)
+    ben.add_argument("--prompt-lengths", default="1,8,16",
+                     help="prompt lengths, taken in turn by the requests")
+    ben.add_argument("--max-new-tokens", type=int, default=4)
+    ben.add_argument("--rate-rps", type=float, default=100.0,
+                     help="Poisson arrivals at this rate; 0: all requests at once")
+    ben.add_argument("--seed", type=int, default=42, help="seed of prompts and arrivals")
+    ben.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    ben.add_argument("--block-size", type=int, default=16, help="tokens in a page of the cache")
+    ben.add_argument("--num-blocks", type=int, default=None, help="pages in the pool")
+    ben.add_argument("--max-batch-tokens", type=int, default=2048, help="token budget of a step")
+    ben.add_argument("--device", default="cuda:0")
+    ben.set_defaults(run=_bench)
 
     rep = sub.add_parser("replay", help="trace replay (same as bin/trace_run)")
     rep.add_argument("--model", required=True)

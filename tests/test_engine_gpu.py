@@ -178,6 +178,34 @@ def test_command_line(model_root):
     assert lines == [f"Generated token IDs: {w}" for w in want]
 
 
+def test_command_line_bench(model_root, tmp_path):
+    """The request-level benchmark: the reference's smoke request set through the engine, twice;
+    every request completes with its four tokens, the figures are consistent with one another, and
+    an existing output folder is refused."""
+    import json
+    spec, folder, config, weights, prompts = _setup("tiny_a", model_root)
+    out = tmp_path / "bench-out"
+    command = [sys.executable, "-m", "distengine_b200", "bench", "--model", folder, "--dtype",
+               "float32", "--repeats", "2", "--output", str(out), "--num-blocks", "64",
+               "--block-size", str(spec["page_size"])]
+    proc = subprocess.run(command, capture_output=True, text=True, cwd=ROOT, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert f"Saved {out / 'baseline.json'}" in proc.stdout
+    report = json.loads((out / "baseline.json").read_text())
+    assert report["executed_repeats"] == 2 and len(report["runs"]) == 2
+    assert report["workload"]["prompt_lengths"] == [1, 8, 16]
+    for run in report["runs"]:
+        assert run["completed"] == 6 and run["output_tokens"] == 24
+        assert run["completed_output_tokens_per_s"] == pytest.approx(24 / run["elapsed_s"])
+        for row in run["per_request"].values():
+            assert row["output_tokens"] == 4
+            assert 0 < row["ttft_s"] <= row["e2e_s"] and row["tpot_s"] >= 0
+        assert run["latencies"]["e2e_s"]["p50"] <= run["latencies"]["e2e_s"]["p99"]
+    assert report["aggregate"]["request_throughput_rps"]["mean"] > 0
+    again = subprocess.run(command, capture_output=True, text=True, cwd=ROOT, timeout=600)
+    assert again.returncode != 0 and "Choose a new output directory" in again.stderr
+
+
 def test_no_cpu_path():
     from distengine_b200.kernels import KernelsUnavailable
     from distengine_b200.models import load_model
