@@ -37,7 +37,7 @@ def available() -> "str | None":
 
 
 def run(model: dict, batch: int, prompt_len: int, steps: int, warmup: int, prefill_len: int,
-        points: "tuple[int, ...]" = (1, 64), page: int = 16, seed: int = 0) -> dict:
+        points: "tuple[int, ...]" = (1, 16, 64), page: int = 16, seed: int = 0) -> dict:
     sys.path.insert(0, REF)
     import torch
     from transformers import LlamaConfig
