@@ -89,6 +89,13 @@ def test_decode_split_takes_sizes_between_the_powers_of_two():
     assert choose_decode_split(20, 4, 520, per_sm=4, sm_count=SMS)[0] == 4       # short ranges: powers of two
 
 
+def test_clusters_of_eight_only_while_a_fifth_of_the_places_stays_free():
+    # 4 kv heads, 4 blocks an SM: 592 places; clusters of 8 up to 473 blocks (14 sequences: 448)
+    for sequences, want in ((8, 8), (12, 8), (14, 8), (15, 4), (16, 4), (18, 4), (32, 4), (37, 4),
+                            (38, 2), (64, 2)):
+        assert choose_decode_split(sequences, 4, 640, per_sm=4, sm_count=SMS)[0] == want, sequences
+
+
 def test_chunk_choice_fills_the_gpu_or_leaves_ranges_whole():
     assert choose_chunk(1000, 4, 4096, sm_count=SMS) == 0                  # enough tiles: no split
     c = choose_chunk(8, 4, 4096, sm_count=SMS)
