@@ -50,6 +50,10 @@ class KernelStatusError(RuntimeError):
     """A kernel found an index it could not use (a position without a page) and skipped work."""
 
 
+MAX_GRAPHS = 128        # shapes of steps kept as CUDA graphs at a time
+PORTION_REPEATS = 3     # a step with prompt portions is shaped for replay after this many like it
+
+
 def _align(n: int) -> int:
     return (n + 3) & ~3
 
@@ -75,8 +79,11 @@ class StepRunner:
         self.use_graphs = use_graphs
         self.steps_run = 0
         self.last_arrays: dict[str, torch.Tensor] = {}
-        # decode steps replayed as CUDA graphs: key -> (graph, logits, kernels in it, generation)
+        # steps replayed as CUDA graphs: key -> (graph, logits, kernels in it, generation)
         self._graphs: dict[tuple, tuple] = {}
+        # how often a shape of step with prompt portions has come (such a step is shaped for
+        # replay once it has come PORTION_REPEATS times; steps of single tokens always are)
+        self._portion_shapes: dict[tuple, int] = {}
         self._meta_generation = 0
         self._layouts: dict[tuple, tuple] = {}
         self.graph_replays = 0
@@ -192,12 +199,25 @@ class StepRunner:
             raise
         host = self._host_arrays(entries)
         graph_shape = None
-        if (self.use_graphs and int(host.seq_qlen.max()) == 1
-                and getattr(self.model, "graph_safe", True)):
-            # a pure decode step: shape its arrays by the batch's shape only, so that it can be
-            # replayed; the key range is capped at the next multiple of 512 positions
-            longest = int(host.seq_pos0.max()) + 1
-            graph_shape = {"context_cap": (longest + 511) // 512 * 512}
+        if self.use_graphs and getattr(self.model, "graph_safe", True):
+            # shape the step's arrays by the batch's shape only, so that it can be replayed; the
+            # key range is capped at the next multiple of 512 positions.  Every step of single
+            # tokens; a step with prompt portions once the same portions (their lengths, the cap,
+            # the wanted rows) have come PORTION_REPEATS times - a long prompt's full portions, a
+            # benchmark's prompts - since shaping costs padding and a capture costs more than a
+            # step (measured: requests of random lengths through the scheduler, every shape
+            # twice, lose 7 % when the second coming is already shaped and the third captured)
+            longest = int((host.seq_pos0.astype(np.int64) + host.seq_qlen).max())
+            cap = (longest + 511) // 512 * 512
+            if int(host.seq_qlen.max()) == 1:
+                graph_shape = {"context_cap": cap}
+            else:
+                shape = (host.seq_qlen.tobytes(), cap, len(host.logit_rows))
+                if len(self._portion_shapes) > 512 and shape not in self._portion_shapes:
+                    self._portion_shapes.clear()
+                count = self._portion_shapes[shape] = self._portion_shapes.get(shape, 0) + 1
+                if count > PORTION_REPEATS:
+                    graph_shape = {"context_cap": cap}
         prep = StepPrep(host, graph_shape)
         self.model.prepare(prep)
         for name, array in (extra or {}).items():
@@ -271,11 +291,11 @@ class StepRunner:
             e.tokens = [t]
 
     def _forward_graphed(self, ctx: StepContext, prep: StepPrep, graph_shape: dict) -> torch.Tensor:
-        """Replay the decode step of this shape as a CUDA graph; the first step of a shape runs
+        """Replay the step of this shape as a CUDA graph; the first step of a shape runs
         as it is (which also brings every scratch buffer to its size), the second is captured.
         The graph reads the step's arrays from the same device addresses every time; only their
         contents change."""
-        key = (ctx.n_seqs, graph_shape["context_cap"], ctx.logit_rows.shape[0],
+        key = (ctx.host.seq_qlen.tobytes(), graph_shape["context_cap"], ctx.logit_rows.shape[0],
                tuple((name, array.shape) for name, array in prep.extra.items()),
                tuple(sorted(prep.notes.items())))
         stamp = (self.workspace.generation, self._meta_generation)
@@ -284,6 +304,8 @@ class StepRunner:
             self._graphs.clear()                       # buffers moved: every graph is stale
             entry = None
         if entry is None:
+            if len(self._graphs) >= MAX_GRAPHS:        # steps of ever new shapes: start over
+                self._graphs.clear()
             logits = self.model.forward(ctx, self.bindings)
             self._graphs[key] = (None, logits, 0, (self.workspace.generation,
                                                     self._meta_generation))

@@ -123,7 +123,11 @@ def test_graphed_decode_steps_at_the_benchmark_width(batch, model_root):
     with tempfile.TemporaryDirectory() as out:
         th.replay_in_process(runner, steps, out)
         rows = th.collect(steps, out, VOCAB)
-    assert runner.graph_replays >= new - 4 and len(runner._graphs) == 2
+    # (a graph's key begins with the sequences' token counts; steps of the prompts, which repeat
+    # too, may have graphs of their own)
+    decode_graphs = [key for key in runner._graphs
+                     if (np.frombuffer(key[0], dtype=np.int32) == 1).all()]
+    assert runner.graph_replays >= new - 4 and len(decode_graphs) == 2
     positions = list(range(prompt_len, prompt_len + new))
     for rid, tokens in requests.items():
         want = _plain_rows(model_root, tokens, torch.bfloat16, positions)

@@ -251,6 +251,57 @@ def test_replay_with_graphs_matches_plain(name, dtype_name, schedule, model_root
                      f"{name} graphs {schedule} {rid}")
 
 
+@pytest.mark.parametrize("name", ["tiny_b", "tiny_d"])
+@pytest.mark.parametrize("dtype_name", ["float32", "bfloat16"])
+def test_steps_with_prompt_portions_of_a_shape_seen_before_are_replayed(name, dtype_name,
+                                                                        model_root):
+    """A step with prompt portions is replayed as a CUDA graph once its shape (the portions'
+    lengths, the cap on positions, the wanted rows) has come a few times: eight prompts of 70
+    tokens, one a step, on pages that are used again; then seven steps of two new prompts each
+    (40 and 9 tokens); then a prompt of 105 tokens in seven portions of 15.  Every logit row
+    against the plain implementation; in 32-bit also bit for bit against the same trace without
+    graphs."""
+    from distengine_b200.engine.replay import build_runner
+    folder, config, _, _ = _model(name, model_root)
+    dtype = DTYPES[dtype_name]
+    prompts, steps = {}, []
+
+    def step(entries, end):
+        steps.append({"step": len(steps), "entries": entries, "end": end})
+
+    for i in range(8):
+        prompts[f"a{i}"] = tiny_configs.prompt_tokens(name, 70, 20 + i)
+        step([{"id": f"a{i}", "tokens": prompts[f"a{i}"], "want": [0, 35, 69]}], [f"a{i}"])
+    for i in range(7):
+        prompts[f"b{i}"] = tiny_configs.prompt_tokens(name, 40, 40 + i)
+        prompts[f"c{i}"] = tiny_configs.prompt_tokens(name, 9, 60 + i)
+        step([{"id": f"b{i}", "tokens": prompts[f"b{i}"], "want": [39]},
+              {"id": f"c{i}", "tokens": prompts[f"c{i}"], "want": [0, 8]}], [f"b{i}", f"c{i}"])
+    prompts["d"] = tiny_configs.prompt_tokens(name, 105, 80)
+    for part in range(7):
+        step([{"id": "d", "tokens": prompts["d"][15 * part: 15 * part + 15], "want": [14]}],
+             ["d"] if part == 6 else [])
+    results = {}
+    for graphs in (True, False):
+        runner = build_runner(folder, dtype_name, 128,
+                              page_size=tiny_configs.ALL[name]["page_size"],
+                              poison_freed_pages=True, use_graphs=graphs)
+        with tempfile.TemporaryDirectory() as out:
+            th.replay_in_process(runner, steps, out)
+            results[graphs] = th.collect(steps, out, config["vocab_size"])
+        runner.cache.check_invariants()
+        if graphs:
+            # a shape's first three steps run as they are, the fourth shaped for replay, the
+            # fifth is captured and replayed
+            assert runner.graph_replays == 4 + 3 + 3
+    weights = plain.load_model_folder(folder)[1]
+    for (rid, position), got in results[True].items():
+        want = plain.plain_forward(config, weights, prompts[rid], dtype).numpy()[position]
+        assert_close(got[None], want[None], dtype, f"{name} graphed portions {rid} {position}")
+        if dtype_name == "float32":
+            assert np.array_equal(got, results[False][(rid, position)]), (rid, position)
+
+
 @pytest.mark.parametrize("name", ["tiny_d", "tiny_e"])
 @pytest.mark.parametrize("dtype_name", ["float32", "bfloat16"])
 @pytest.mark.parametrize("schedule", ["whole", "portions", "mixed_tight"])
