@@ -64,8 +64,8 @@ def _generate(args: argparse.Namespace) -> int:
 
 
 def _bench(args: argparse.Namespace) -> int:
-    if args.repeats <= 0:
-        raise SystemExit("--repeats must be positive")
+    if args.repeats <= 0 or args.warmup_requests <= 0:
+        raise SystemExit("--repeats and --warmup-requests must be positive")
     if os.path.exists(args.output):
         raise SystemExit("Choose a new output directory")
     return _with_model_folder(args, _bench_from_folder)
@@ -83,17 +83,20 @@ def _bench_from_folder(args: argparse.Namespace) -> int:
     engine = Engine(args.model, config)
     workload = benchmark.make_workload(args.num_requests, lengths, args.max_new_tokens,
                                        engine.model.config.vocabulary, args.seed, args.rate_rps)
-    # once unmeasured: kernels are compiled and loaded, buffers sized, decode steps captured
-    benchmark.run_workload(engine, [benchmark.BenchRequest(f"warm-{r.request_id}", 0.0,
-                                                           r.prompt_token_ids, r.max_new_tokens)
-                                    for r in workload])
+    # before every measured run, unmeasured: copies of the longest request, as the reference does
+    # (src/utils/benchmark.py:311-323); the first of them also compiles and loads the kernels
+    longest = max(workload, key=lambda r: len(r.prompt_token_ids))
     runs = []
     for repeat in range(args.repeats):
+        benchmark.run_workload(engine, [
+            benchmark.BenchRequest(f"warmup-{repeat}-{i}", 0.0, longest.prompt_token_ids,
+                                   longest.max_new_tokens) for i in range(args.warmup_requests)])
         named = [benchmark.BenchRequest(f"run{repeat}-{r.request_id}", r.arrival_s,
                                         r.prompt_token_ids, r.max_new_tokens) for r in workload]
         runs.append(benchmark.run_workload(engine, named))
     report = {
         "workload": {"num_requests": args.num_requests, "prompt_lengths": lengths,
+                     "warmup_requests": args.warmup_requests,
                      "max_new_tokens": args.max_new_tokens, "rate_rps": args.rate_rps,
                      "seed": args.seed, "arrival_mode": "poisson" if args.rate_rps > 0 else "burst"},
         "engine": {"model": os.path.abspath(args.model), "dtype": args.dtype,
@@ -207,6 +210,8 @@ def main(argv: "list[str] | None" = None) -> int:
     ben.add_argument("--output", required=True, help="a new folder; receives baseline.json")
     ben.add_argument("--decode-batch-size", type=int, default=64,
                      help="most requests decoded together in one step")
+    ben.add_argument("--warmup-requests", type=int, default=4,
+                     help="copies of the longest request run before every measured run")
     ben.add_argument("--num-requests", type=int, default=6)
     ben.add_argument("--prompt-lengths", default="1,8,16",
                      help="prompt lengths, taken in turn by the requests")
